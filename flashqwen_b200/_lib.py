@@ -1,0 +1,82 @@
+"""ctypes loader for libfqb.so. Fails loudly when the library has not been built."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_NAME = "libfqb.so"
+
+
+class FqbError(RuntimeError):
+    def __init__(self, code, where, text):
+        super().__init__(f"{where}: {text} (code {code})")
+        self.code = code
+
+
+def library_path():
+    return os.path.join(_HERE, _NAME)
+
+
+def _load():
+    path = library_path()
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python flashqwen_b200/build.py` "
+            "(nvcc, sm_100a). There is no fallback implementation."
+        )
+    return C.CDLL(path)
+
+
+lib = _load()
+
+_i, _i64, _u64, _f, _p = C.c_int, C.c_int64, C.c_uint64, C.c_float, C.c_void_p
+_pi = C.POINTER(C.c_int32)
+
+# every symbol include/fqb.h declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "fqb_version": (C.c_char_p, []),
+    "fqb_strerror": (C.c_char_p, [_i]),
+    "fqb_last_error": (C.c_char_p, []),
+    "fqb_kv_layout_query": (_i, [_i, _p]),
+    "fqb_kv_pool_bytes": (_i64, [_i, _i]),
+    "fqb_kv_append": (_i, [_p, _i, _i, _p, _i, _i, _i, _p, _i, _p, _p, _i, _p]),
+    "fqb_norm_rope_append": (_i, [_p, _i, _i, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _f, _p, _i, _p, _p, _i, _p]),
+    "fqb_attn_decode_partial_slots": (_i64, [_i, _i, _i]),
+    "fqb_attn_decode": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64, _p]),
+    "fqb_attn_prefill": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
+    "fqb_copy_blocks": (_i, [_p, _i, _i, _p, _i, _p]),
+    "fqb_copy_blocks_layers": (_i, [_p, _i, _i, _i, _p, _i, _p]),
+    "fqb_gather_blocks": (_i, [_p, _i, _i, _p, _i, _p, _p]),
+    "fqb_scatter_blocks": (_i, [_p, _i, _i, _p, _i, _p, _p]),
+    "fqb_device_status": (_i, [_pi]),
+    "fqb_device_status_reset": (_i, []),
+    "fqb_alloc_create": (_p, [_i]),
+    "fqb_alloc_destroy": (None, [_p]),
+    "fqb_alloc_num_blocks": (_i, [_p]),
+    "fqb_alloc_num_free": (_i, [_p]),
+    "fqb_alloc_blocks_for": (_i, [_i]),
+    "fqb_alloc_refcount": (_i, [_p, _i]),
+    "fqb_alloc_block_hash": (_u64, [_p, _i]),
+    "fqb_alloc_one": (_i, [_p]),
+    "fqb_alloc_free_one": (_i, [_p, _i]),
+    "fqb_alloc_free_table": (_i, [_p, _pi, C.POINTER(_i)]),
+    "fqb_alloc_grow": (_i, [_p, _pi, C.POINTER(_i), _i, _i]),
+    "fqb_alloc_cache_lookup": (_i, [_p, _u64]),
+    "fqb_alloc_cache_insert": (_i, [_p, _i, _u64]),
+    "fqb_hash_block": (_u64, [_u64, _pi, _i]),
+    "fqb_acquire_prefix": (_i, [_p, _pi, _i, _pi, _i, C.POINTER(_u64)]),
+    "fqb_cache_blocks": (_i, [_p, _pi, _i, _pi, _i, C.POINTER(_u64)]),
+    "fqb_cow_prepare": (_i, [_p, _pi, _i, _pi]),
+    "fqb_step_pack": (_i, [_pi, _i, _i, C.POINTER(_pi), _pi, _i, _pi, _pi, _pi, _pi, _pi, _pi]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = header and library disagree
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(code, where):
+    """Raises FqbError for a negative status code; returns the code otherwise."""
+    if code < 0:
+        raise FqbError(code, where, lib.fqb_last_error().decode() or lib.fqb_strerror(code).decode())
+    return code

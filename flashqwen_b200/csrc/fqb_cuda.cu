@@ -1,0 +1,373 @@
+// libfqb, CUDA side: the extern "C" operators declared in include/fqb.h. Host code here only
+// validates scalar arguments, builds the TMA descriptor of the cache and enqueues kernels on the
+// caller's stream; it allocates nothing and never synchronises (fqb_device_status excepted).
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "blocks.cuh"
+#include "common.cuh"
+#include "decode.cuh"
+#include "errors.h"
+#include "kv_append.cuh"
+#include "prefill.cuh"
+
+namespace fqb {
+namespace {
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return set_error(FQB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+#define FQB_CUDA_TRY(call)                                   \
+  do {                                                       \
+    cudaError_t e_ = (call);                                 \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call);      \
+  } while (0)
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct DeviceInfo {
+  int sm_count = 0;
+};
+int device_info(DeviceInfo& out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(mu);
+  if (dev < 0 || dev >= 64) return set_error(FQB_ERR_CUDA, "device ordinal %d out of range", dev);
+  if (cache[dev].sm_count == 0) {
+    int n = 0;
+    FQB_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    cache[dev].sm_count = n;
+  }
+  out = cache[dev];
+  return FQB_OK;
+}
+
+// ---- TMA descriptor of one layer's cache ------------------------------------------------------
+// The cache [num_blocks][2][16][row_elems] is described as a 5-D tensor whose innermost
+// dimension is 64 bf16 (128 bytes, the widest row the 128-byte swizzle takes):
+//   d0 = 64 dims, d1 = 16 tokens, d2 = row_elems/64 half-heads, d3 = 2 planes, d4 = blocks.
+// One box {64,16,2,2,1} is the K and V slice of one kv head of one page (8 KiB) and lands in
+// shared memory as [plane][half][token][64] with rows of 128 bytes, which ldmatrix then reads
+// without bank conflicts.
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+int get_encode(EncodeFn& fn) {
+  static EncodeFn cached = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cached) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    FQB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !p)
+      return set_error(FQB_ERR_CUDA, "cuTensorMapEncodeTiled not available from this driver");
+    cached = reinterpret_cast<EncodeFn>(p);
+  }
+  fn = cached;
+  return FQB_OK;
+}
+
+int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtensorMap& map) {
+  struct Entry {
+    const void* ptr;
+    int nb, kvh;
+    CUtensorMap map;
+  };
+  constexpr int kCache = 128;
+  static thread_local Entry lru[kCache];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i)
+    if (lru[i].ptr == cache && lru[i].nb == num_blocks && lru[i].kvh == kv_heads_local) {
+      map = lru[i].map;
+      return FQB_OK;
+    }
+  EncodeFn enc;
+  if (int rc = get_encode(enc)) return rc;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(kv_heads_local) * kHd * 2;
+  cuuint64_t dims[5] = {64, static_cast<cuuint64_t>(kTok), static_cast<cuuint64_t>(kv_heads_local) * 2, 2,
+                        static_cast<cuuint64_t>(num_blocks)};
+  cuuint64_t strides[4] = {row_bytes, 128, row_bytes * kTok, row_bytes * kTok * 2};
+  cuuint32_t box[5] = {64, static_cast<cuuint32_t>(kTok), 2, 2, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(FQB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  Entry& e = lru[next];
+  e.ptr = cache;
+  e.nb = num_blocks;
+  e.kvh = kv_heads_local;
+  e.map = map;
+  next = (next + 1) % kCache;
+  if (used < kCache) ++used;
+  return FQB_OK;
+}
+
+int check_attn_shape(int n_heads, int n_kv, int head_dim, int block_size) {
+  if (head_dim != kHd) return set_error(FQB_ERR_SHAPE, "head_dim %d: only 128 is supported", head_dim);
+  if (block_size != kTok) return set_error(FQB_ERR_SHAPE, "block_size %d: only 16 is supported", block_size);
+  if (n_kv <= 0 || n_heads != n_kv * kGroup)
+    return set_error(FQB_ERR_SHAPE, "n_heads %d / n_kv %d: the GQA group must be 4", n_heads, n_kv);
+  return FQB_OK;
+}
+
+// ---- decode configurations -----------------------------------------------------------------------
+// A: 8 warps x 3 page buffers, one CTA per SM (192 KiB of loads in flight per SM).
+// B: 4 warps x 3 page buffers, two CTAs per SM.
+// FQB_DECODE_CONFIG=A|B picks one at process start (tuning aid); the default is what measured best.
+struct DecodeCfgA { static constexpr int NW = 8, NS = 3, MINB = 1, MAXD = 512; };
+struct DecodeCfgB { static constexpr int NW = 4, NS = 3, MINB = 2, MAXD = 256; };
+
+char decode_config() {
+  static char c = 0;
+  if (!c) {
+    const char* e = std::getenv("FQB_DECODE_CONFIG");
+    c = (e && (e[0] == 'A' || e[0] == 'B')) ? e[0] : 'A';
+  }
+  return c;
+}
+
+template <class Cfg>
+int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n_decode, int sm_count,
+                  cudaStream_t st) {
+  using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD>;
+  auto kern = decode_split_kernel<Cfg::NW, Cfg::NS, Cfg::MINB, Cfg::MAXD>;
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    attr_dev = dev;
+  }
+  const int grid = sm_count * Cfg::MINB;
+  for (int base = 0; base < n_decode; base += Cfg::MAXD) {
+    P.rids = rids + base;
+    P.n_decode = n_decode - base < Cfg::MAXD ? n_decode - base : Cfg::MAXD;
+    const long long need = (static_cast<long long>(P.n_decode) * P.n_kv + grid) * kGroup + P.n_decode + 1;
+    if (need > P.partial_slots)
+      return set_error(FQB_ERR_WORKSPACE, "decode scratch: %lld partial slots needed, %lld given", need,
+                       P.partial_slots);
+    kern<<<grid, Cfg::NW * 32, L::kAlloc, st>>>(map, P);
+    decode_combine_kernel<<<P.n_decode * P.n_kv, 128, 0, st>>>(P);
+  }
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+}  // namespace
+}  // namespace fqb
+
+using namespace fqb;
+
+extern "C" {
+
+const char* fqb_version(void) { return "libfqb 0.1 (sm_100a)"; }
+
+int fqb_kv_append(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                  int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row,
+                  const int32_t* pos, int M, void* stream) {
+  if (M <= 0) return FQB_OK;
+  if (!cache || !qkv || !bt || !bt_row || !pos) return set_error(FQB_ERR_INVALID, "kv_append: null pointer");
+  if (num_blocks <= 0 || kv_heads_local <= 0 || bt_stride <= 0)
+    return set_error(FQB_ERR_INVALID, "kv_append: non-positive size");
+  if (!aligned16(cache) || !aligned16(qkv) || (src_stride % 8) || (k_off % 8) || (v_off % 8))
+    return set_error(FQB_ERR_INVALID, "kv_append: pointers, src_stride, k_off and v_off must keep 16-byte alignment");
+  AppendParams P{static_cast<__nv_bfloat16*>(cache), num_blocks, kv_heads_local * kHd,
+                 static_cast<const __nv_bfloat16*>(qkv), src_stride, k_off, v_off, bt, bt_stride, bt_row, pos, M};
+  kv_append_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_heads_local, void* qkv,
+                         int src_stride, int q_off, int k_off, int v_off, const float* wq, const float* wk,
+                         const float* cos_tab, const float* sin_tab, float eps, const int32_t* bt,
+                         int bt_stride, const int32_t* bt_row, const int32_t* pos, int M, void* stream) {
+  if (M <= 0) return FQB_OK;
+  if (!cache || !qkv || !bt || !bt_row || !pos || !wq || !wk || !cos_tab || !sin_tab)
+    return set_error(FQB_ERR_INVALID, "norm_rope_append: null pointer");
+  if (num_blocks <= 0 || kv_heads_local <= 0 || q_heads_local < 0 || bt_stride <= 0)
+    return set_error(FQB_ERR_INVALID, "norm_rope_append: non-positive size");
+  if (!aligned16(cache) || !aligned16(qkv) || (src_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8) ||
+      (reinterpret_cast<uintptr_t>(cos_tab) & 7u) || (reinterpret_cast<uintptr_t>(sin_tab) & 7u) ||
+      (reinterpret_cast<uintptr_t>(wq) & 7u) || (reinterpret_cast<uintptr_t>(wk) & 7u))
+    return set_error(FQB_ERR_INVALID, "norm_rope_append: misaligned pointer or offset");
+  NormRopeParams P;
+  P.a = AppendParams{static_cast<__nv_bfloat16*>(cache), num_blocks, kv_heads_local * kHd,
+                     static_cast<const __nv_bfloat16*>(qkv), src_stride, k_off, v_off, bt, bt_stride, bt_row, pos, M};
+  P.q_heads = q_heads_local;
+  P.kv_heads = kv_heads_local;
+  P.q_off = q_off;
+  P.wq = wq;
+  P.wk = wk;
+  P.cos_tab = cos_tab;
+  P.sin_tab = sin_tab;
+  P.eps = eps;
+  norm_rope_append_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks) {
+  (void)max_blocks;  // the split count follows the SM count, not the context length
+  if (max_decode <= 0 || n_heads_local <= 0) return 0;
+  // (pairs + CTAs) * 4 heads + per-sequence partition record; 2 CTAs per SM on up to 256 SMs
+  return (static_cast<int64_t>(max_decode) * (n_heads_local / kGroup) + 512) * kGroup + max_decode + 1;
+}
+
+int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                    int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
+                    int n_decode, const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                    float* pl, float* pa, int64_t partial_slots, void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
+  if (!q || !cache || !out || !pos || !qstart || !decode_rids || !bt || !pm || !pl || !pa)
+    return set_error(FQB_ERR_INVALID, "attn_decode: null pointer");
+  if (num_blocks <= 0 || max_blocks <= 0 || partial_slots <= 0)
+    return set_error(FQB_ERR_INVALID, "attn_decode: non-positive size");
+  if (!aligned16(q) || !aligned16(cache) || !aligned16(out) || !aligned16(pa) || (q_stride % 8))
+    return set_error(FQB_ERR_INVALID, "attn_decode: q, cache, out, pa and q_stride must keep 16-byte alignment");
+  DeviceInfo di;
+  if (int rc = device_info(di)) return rc;
+  CUtensorMap map;
+  if (int rc = make_cache_map(cache, num_blocks, n_kv, map)) return rc;
+  DecodeParams P;
+  P.q = static_cast<const __nv_bfloat16*>(q);
+  P.q_stride = q_stride;
+  P.out = static_cast<__nv_bfloat16*>(out);
+  P.n_heads = n_heads;
+  P.n_kv = n_kv;
+  P.pos = pos;
+  P.qstart = qstart;
+  P.rids = decode_rids;
+  P.n_decode = n_decode;
+  P.bt = bt;
+  P.max_blocks = max_blocks;
+  P.num_blocks = num_blocks;
+  P.scale_log2 = scale * kLog2e;
+  P.pm = pm;
+  P.pl = pl;
+  P.pa = pa;
+  P.partial_slots = partial_slots;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (decode_config() == 'B') return launch_decode<DecodeCfgB>(map, P, decode_rids, n_decode, di.sm_count, st);
+  return launch_decode<DecodeCfgA>(map, P, decode_rids, n_decode, di.sm_count, st);
+}
+
+int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                     int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart, const int32_t* qlen,
+                     const int32_t* rids, int R, int max_qlen, const int32_t* bt, int max_blocks, int block_size,
+                     float scale, void* stream) {
+  if (R <= 0) return FQB_OK;
+  if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
+  if (!q || !cache || !out || !pos || !qstart || !qlen || !rids || !bt)
+    return set_error(FQB_ERR_INVALID, "attn_prefill: null pointer");
+  if (num_blocks <= 0 || max_blocks <= 0 || max_qlen <= 0)
+    return set_error(FQB_ERR_INVALID, "attn_prefill: non-positive size");
+  if ((reinterpret_cast<uintptr_t>(q) & 3u) || !aligned16(cache) || (reinterpret_cast<uintptr_t>(out) & 3u) ||
+      (q_stride % 2))
+    return set_error(FQB_ERR_INVALID, "attn_prefill: misaligned pointer or stride");
+  if (n_kv > 65535 || R > 65535) return set_error(FQB_ERR_SHAPE, "attn_prefill: n_kv or R above 65535");
+  CUtensorMap map;
+  if (int rc = make_cache_map(cache, num_blocks, n_kv, map)) return rc;
+  PrefillParams P;
+  P.q = static_cast<const __nv_bfloat16*>(q);
+  P.q_stride = q_stride;
+  P.out = static_cast<__nv_bfloat16*>(out);
+  P.n_heads = n_heads;
+  P.n_kv = n_kv;
+  P.pos = pos;
+  P.qstart = qstart;
+  P.qlen = qlen;
+  P.rids = rids;
+  P.bt = bt;
+  P.max_blocks = max_blocks;
+  P.num_blocks = num_blocks;
+  P.scale_log2 = scale * kLog2e;
+  constexpr int RT = 2, NS = 6, MINB = 1;
+  using C = PrefillCfg<RT, NS>;
+  auto kern = prefill_kernel<RT, NS, MINB>;
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr_dev = dev;
+  }
+  dim3 grid((max_qlen + C::kBM - 1) / C::kBM, n_kv, R);
+  kern<<<grid, C::kThreads, C::kSmem, static_cast<cudaStream_t>(stream)>>>(map, P);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+static int block_move(void* const* layers, int n_layers, void* cache, void* lin, int num_blocks,
+                      int kv_heads_local, const int32_t* idx, int n, int mode, void* stream, const char* who) {
+  if (n <= 0) return FQB_OK;
+  if ((!cache && !layers) || !idx || (mode != 0 && !lin)) return set_error(FQB_ERR_INVALID, "%s: null pointer", who);
+  if (num_blocks <= 0 || kv_heads_local <= 0 || n_layers <= 0)
+    return set_error(FQB_ERR_INVALID, "%s: non-positive size", who);
+  if ((cache && !aligned16(cache)) || (lin && !aligned16(lin)))
+    return set_error(FQB_ERR_INVALID, "%s: misaligned pointer", who);
+  if (n_layers > 65535) return set_error(FQB_ERR_SHAPE, "%s: more than 65535 layers", who);
+  BlockMoveParams P;
+  P.layers = layers;
+  P.cache = static_cast<uint4*>(cache);
+  P.lin = static_cast<uint4*>(lin);
+  P.idx = idx;
+  P.n = n;
+  P.num_blocks = num_blocks;
+  P.block_vecs = FQB_PLANES * kTok * kv_heads_local * kHd / 8;
+  P.mode = mode;
+  dim3 grid(n, (P.block_vecs + kCopyChunkVecs - 1) / kCopyChunkVecs, n_layers);
+  block_move_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+int fqb_copy_blocks(void* cache, int num_blocks, int kv_heads_local, const int32_t* pairs, int n_pairs,
+                    void* stream) {
+  return block_move(nullptr, 1, cache, nullptr, num_blocks, kv_heads_local, pairs, n_pairs, 0, stream,
+                    "copy_blocks");
+}
+int fqb_copy_blocks_layers(void* const* layer_caches, int n_layers, int num_blocks, int kv_heads_local,
+                           const int32_t* pairs, int n_pairs, void* stream) {
+  if (n_pairs > 0 && !layer_caches) return set_error(FQB_ERR_INVALID, "copy_blocks_layers: null pointer");
+  return block_move(layer_caches, n_layers, nullptr, nullptr, num_blocks, kv_heads_local, pairs, n_pairs, 0,
+                    stream, "copy_blocks_layers");
+}
+int fqb_gather_blocks(const void* cache, int num_blocks, int kv_heads_local, const int32_t* list, int n,
+                      void* out, void* stream) {
+  return block_move(nullptr, 1, const_cast<void*>(cache), out, num_blocks, kv_heads_local, list, n, 1, stream,
+                    "gather_blocks");
+}
+int fqb_scatter_blocks(void* cache, int num_blocks, int kv_heads_local, const int32_t* list, int n,
+                       const void* in, void* stream) {
+  return block_move(nullptr, 1, cache, const_cast<void*>(in), num_blocks, kv_heads_local, list, n, 2, stream,
+                    "scatter_blocks");
+}
+
+int fqb_device_status(int32_t* detail) {
+  int h[4] = {0, 0, 0, 0};
+  FQB_CUDA_TRY(cudaMemcpyFromSymbol(h, g_status, sizeof(h)));
+  if (detail) std::memcpy(detail, h, sizeof(h));
+  if (h[0] != 0)
+    return set_error(h[0], "device status: code %d from kernel %d, block %d, value %d", h[0], h[1], h[2], h[3]);
+  return FQB_OK;
+}
+
+int fqb_device_status_reset(void) {
+  const int z[4] = {0, 0, 0, 0};
+  FQB_CUDA_TRY(cudaMemcpyToSymbol(g_status, z, sizeof(z)));
+  return FQB_OK;
+}
+
+}  // extern "C"

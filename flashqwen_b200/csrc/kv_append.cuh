@@ -1,0 +1,132 @@
+// Kernel 1: KV append through the block table, and its fused form with per-head RMSNorm + RoPE.
+//
+// Semantics follow the reference's StoreKvKernel (engine/src/kv_store.cu:48-64 of the FlashQwen
+// tree) and HeadNormRopeKernel (engine/src/kernels.cu:97-131). The reference moves one 2-byte
+// element per thread with two integer divisions and three dependent index loads each; here one
+// CTA takes one token row, looks its page up once, and moves the row with 16-byte loads/stores.
+#pragma once
+
+#include "common.cuh"
+
+namespace fqb {
+
+struct AppendParams {
+  __nv_bfloat16* cache;
+  int num_blocks;
+  int row_elems;  // kv_heads_local * 128
+  const __nv_bfloat16* qkv;
+  int src_stride, k_off, v_off;
+  const int* bt;
+  int bt_stride;
+  const int* bt_row;
+  const int* pos;
+  int M;
+};
+
+// Element offset of token slot (block, pos%16) of the K plane; the V plane is plane_elems later.
+__device__ __forceinline__ bool append_dst(const AppendParams& P, int m, int kid, long long& dst) {
+  const int p = P.pos[m];
+  const int page = p / kTok;
+  if (p < 0 || page >= P.bt_stride) {
+    report(FQB_ERR_INDEX, kid, p);
+    return false;
+  }
+  const int blk = P.bt[static_cast<long long>(P.bt_row[m]) * P.bt_stride + page];
+  if (static_cast<unsigned>(blk) >= static_cast<unsigned>(P.num_blocks)) {
+    report(FQB_ERR_INDEX, kid, blk);
+    return false;
+  }
+  const long long plane = static_cast<long long>(kTok) * P.row_elems;
+  dst = static_cast<long long>(blk) * FQB_PLANES * plane + static_cast<long long>(p % kTok) * P.row_elems;
+  return true;
+}
+
+__global__ void __launch_bounds__(256)
+kv_append_kernel(const AppendParams P) {
+  const int m = blockIdx.x;
+  long long dst;
+  if (!append_dst(P, m, kKidAppend, dst)) return;
+  const int vecs = P.row_elems / 8;  // 16-byte vectors per plane row
+  const long long plane = static_cast<long long>(kTok) * P.row_elems;
+  const __nv_bfloat16* src = P.qkv + static_cast<long long>(m) * P.src_stride;
+  for (int v = threadIdx.x; v < 2 * vecs; v += blockDim.x) {
+    const int pl = v >= vecs;
+    const int i = v - pl * vecs;
+    const uint4 val = __ldg(reinterpret_cast<const uint4*>(src + (pl ? P.v_off : P.k_off)) + i);
+    *(reinterpret_cast<uint4*>(P.cache + dst + pl * plane) + i) = val;
+  }
+}
+
+struct NormRopeParams {
+  AppendParams a;       // a.qkv is written in place, so the pointer is cast back to mutable
+  int q_heads, kv_heads;
+  int q_off;
+  const float* wq;
+  const float* wk;
+  const float* cos_tab;
+  const float* sin_tab;
+  float eps;
+};
+
+// One warp per head of the row. Lane l holds dims {2l, 2l+1, 64+2l, 65+2l}: the two rotary
+// partners are lane-local and the xor-shuffle butterfly below adds squares in the order
+// (t, t+64), then strides 32, 16, 8, 4, 2, 1 -- the reference's shared-memory halving tree --
+// so an IEEE evaluation is reproducible on the host bit for bit.
+__global__ void __launch_bounds__(256)
+norm_rope_append_kernel(const NormRopeParams P) {
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long dst;
+  const bool ok = append_dst(P.a, m, kKidNormRope, dst);
+  __nv_bfloat16* row = const_cast<__nv_bfloat16*>(P.a.qkv) + static_cast<long long>(m) * P.a.src_stride;
+  const int p = P.a.pos[m];
+  const float2 cs = ok ? __ldg(reinterpret_cast<const float2*>(P.cos_tab + static_cast<long long>(p) * 64) + lane)
+                       : make_float2(1.f, 1.f);
+  const float2 sn = ok ? __ldg(reinterpret_cast<const float2*>(P.sin_tab + static_cast<long long>(p) * 64) + lane)
+                       : make_float2(0.f, 0.f);
+  const int nheads = P.q_heads + P.kv_heads;
+  for (int hd = warp; hd < nheads; hd += 8) {
+    const bool is_k = hd >= P.q_heads;
+    __nv_bfloat16* v = row + (is_k ? P.a.k_off + (hd - P.q_heads) * kHd : P.q_off + hd * kHd);
+    const float* w = is_k ? P.wk : P.wq;
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(v + 2 * lane);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(v + 64 + 2 * lane);
+    const float x0 = __low2float(lo), x1 = __high2float(lo);
+    const float x2 = __low2float(hi), x3 = __high2float(hi);
+    float s0 = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x2, x2));  // dims t, t+64
+    float s1 = __fadd_rn(__fmul_rn(x1, x1), __fmul_rn(x3, x3));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o));
+      s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o));
+    }
+    const float ss = __fadd_rn(s0, s1);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(kHd)), P.eps)));
+    const float2 w_lo = __ldg(reinterpret_cast<const float2*>(w) + lane);
+    const float2 w_hi = __ldg(reinterpret_cast<const float2*>(w + 64) + lane);
+    const float y0 = __fmul_rn(__fmul_rn(x0, inv), w_lo.x), y1 = __fmul_rn(__fmul_rn(x1, inv), w_lo.y);
+    const float y2 = __fmul_rn(__fmul_rn(x2, inv), w_hi.x), y3 = __fmul_rn(__fmul_rn(x3, inv), w_hi.y);
+    const float r0 = __fsub_rn(__fmul_rn(y0, cs.x), __fmul_rn(y2, sn.x));
+    const float r1 = __fsub_rn(__fmul_rn(y1, cs.y), __fmul_rn(y3, sn.y));
+    const float r2 = __fadd_rn(__fmul_rn(y2, cs.x), __fmul_rn(y0, sn.x));
+    const float r3 = __fadd_rn(__fmul_rn(y3, cs.y), __fmul_rn(y1, sn.y));
+    const __nv_bfloat162 out_lo = __floats2bfloat162_rn(r0, r1), out_hi = __floats2bfloat162_rn(r2, r3);
+    if (ok) {
+      *reinterpret_cast<__nv_bfloat162*>(v + 2 * lane) = out_lo;
+      *reinterpret_cast<__nv_bfloat162*>(v + 64 + 2 * lane) = out_hi;
+      if (is_k) {
+        __nv_bfloat16* c = P.a.cache + dst + (hd - P.q_heads) * kHd;
+        *reinterpret_cast<__nv_bfloat162*>(c + 2 * lane) = out_lo;
+        *reinterpret_cast<__nv_bfloat162*>(c + 64 + 2 * lane) = out_hi;
+      }
+    }
+  }
+  if (!ok) return;
+  const int vecs = P.a.row_elems / 8;
+  const long long plane = static_cast<long long>(kTok) * P.a.row_elems;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x)
+    *(reinterpret_cast<uint4*>(P.a.cache + dst + plane) + i) =
+        __ldg(reinterpret_cast<const uint4*>(row + P.a.v_off) + i);
+}
+
+}  // namespace fqb

@@ -1,0 +1,201 @@
+/* fqb.h -- C ABI of libfqb: paged-KV attention operators for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, operator for operator, the paged-KV attention path of the FlashQwen C++
+ * engine. Every entry point names the reference interface it stands in for as
+ * "replaces: <path>:<lines>" (paths inside the FlashQwen tree).
+ *
+ * Conventions (the same ones the reference call sites observe):
+ *   - every data pointer is a DEVICE pointer owned by the caller unless its comment says "host";
+ *   - no entry point allocates device memory, synchronises the device or the stream, or reads
+ *     device data on the host; all work is enqueued on the `stream` argument (a cudaStream_t
+ *     passed as void*), so the calls may be captured into a CUDA graph;
+ *   - launch geometry depends only on scalar arguments, never on context lengths;
+ *   - index arrays are 32-bit int; offsets into the cache are computed in 64 bits;
+ *   - the return value is FQB_OK (0) or a negative FQB_ERR_* code; nothing exits or throws.
+ *     fqb_last_error() gives the text of the calling thread's last failure.
+ *
+ * KV cache layout of one layer on one GPU (bf16):
+ *     cache[num_blocks][2 planes: K, V][16 tokens][kv_heads_local * 128]
+ * kv_heads_local is 8 on a single GPU and 8/G when the KV heads are sharded over G GPUs.
+ */
+#ifndef FQB_H_
+#define FQB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FQB_BLOCK_TOKENS 16 /* replaces: engine/src/kv_layout.h:5 (kKvBlock)  */
+#define FQB_PLANES 2        /* replaces: engine/src/kv_layout.h:7 (kKvPlanes) */
+#define FQB_HEAD_DIM 128    /* engine/src/model_spec.h:15                      */
+#define FQB_GQA_GROUP 4     /* q heads per kv head, engine/src/attn_cute.cu:17 */
+
+enum {
+  FQB_OK = 0,
+  FQB_ERR_INVALID = -1,   /* null pointer, negative size, misaligned pointer            */
+  FQB_ERR_SHAPE = -2,     /* head_dim != 128, group != 4, block_size != 16 and the like  */
+  FQB_ERR_CUDA = -3,      /* a CUDA runtime / driver call failed (text in last_error)     */
+  FQB_ERR_WORKSPACE = -4, /* partial-result scratch too small for this launch            */
+  FQB_ERR_TIMEOUT = -5,   /* device status: a bounded wait inside a kernel ran out       */
+  FQB_ERR_INDEX = -6,     /* device status: a block id / position outside its range      */
+  FQB_ERR_NOMEM = -7,     /* host allocator: block pool exhausted                        */
+  FQB_ERR_STATE = -8      /* host allocator: refcount underflow, unknown block, bad handle */
+};
+
+const char* fqb_version(void);
+const char* fqb_strerror(int code);
+const char* fqb_last_error(void);
+
+/* ---- layout -------------------------------------------------------------------------------
+ * replaces: engine/src/kv_store.h:33-35 (KV / NumBlocks / BlockSize) and the sizing arithmetic
+ * of engine/src/kv_store.cu:21-23. All counts are in bf16 elements unless named *_bytes. */
+typedef struct fqb_kv_layout {
+  int32_t kv_heads_local;
+  int32_t head_dim;
+  int32_t block_tokens;
+  int64_t row_elems;   /* kv_heads_local * 128: one token's K (or V) across local heads */
+  int64_t plane_elems; /* 16 * row_elems                                                  */
+  int64_t block_elems; /* 2 * plane_elems                                                 */
+  int64_t block_bytes; /* block_elems * 2                                                 */
+} fqb_kv_layout;
+
+int fqb_kv_layout_query(int kv_heads_local, fqb_kv_layout* out /* host */);
+int64_t fqb_kv_pool_bytes(int num_blocks, int kv_heads_local);
+
+/* ---- kernel 1: KV append ------------------------------------------------------------------
+ * replaces: engine/src/kv_store.h:29-31 KvStore::StoreKV and engine/src/kv_store.cu:48-75.
+ * For each row m < M copies the K slice qkv[m*src_stride + k_off ..+row_elems) and the V slice
+ * (v_off) into block bt[bt_row[m]*bt_stride + pos[m]/16], token slot pos[m]%16. k_off / v_off
+ * are element offsets of this GPU's first kv head inside the fused row; both, src_stride and the
+ * base pointers must keep 16-byte alignment. M <= 0 is a no-op. */
+int fqb_kv_append(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                  int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row,
+                  const int32_t* pos, int M, void* stream);
+
+/* Fused variant: applies per-head RMSNorm (weights wq / wk, fp32, 128 each) and NeoX rotary
+ * embedding to the q and k heads of every fused row in place, exactly as
+ * engine/src/kernels.cu:97-139 LaunchHeadNormRope does, and appends the resulting K and the
+ * untouched V to the cache as fqb_kv_append does -- one pass over the rows instead of two.
+ * replaces: the pair of calls at engine/src/model_runtime.cu:263-268.
+ * q_heads_local / kv_heads_local heads starting at element offsets q_off / k_off / v_off.
+ * cos_tab / sin_tab are [n_pos][64] fp32 tables (engine/src/model_runtime.cu:111-126). */
+int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_heads_local,
+                         void* qkv, int src_stride, int q_off, int k_off, int v_off,
+                         const float* wq, const float* wk, const float* cos_tab,
+                         const float* sin_tab, float eps, const int32_t* bt, int bt_stride,
+                         const int32_t* bt_row, const int32_t* pos, int M, void* stream);
+
+/* ---- kernel 2: GQA-shared split-K paged decode attention + LSE combine ---------------------
+ * replaces: engine/src/attn_cute.h:14-20 LaunchAttnDecodeCute (engine/src/attn_cute.cu:165-261).
+ * For decode sequence di < n_decode: r = decode_rids[di], flat = qstart[r], qpos = pos[flat];
+ * q head h (row q + flat*q_stride + h*128) attends keys 0..qpos of kv head h/4 through block
+ * table row bt + r*max_blocks; out[(flat*n_heads + h)*128 + d] receives bf16.
+ * n_heads / n_kv are the LOCAL head counts (q already points at this GPU's first head).
+ *
+ * pm, pl (partial_slots floats each) and pa (partial_slots*128 floats) are the split-K scratch,
+ * as at the reference call site (engine/src/model_runtime.cu:191-194, kernels.cuh:33-37).
+ * The split count is decided on the device from the actual context lengths and limited by
+ * partial_slots; fqb_attn_decode_partial_slots() returns a size that never limits it.
+ * num_blocks bounds the block ids (ids outside [0,num_blocks) read zeros and raise
+ * FQB_ERR_INDEX in the device status). n_decode <= 0 is a no-op. */
+int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks);
+
+int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
+                    int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                    const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks,
+                    int block_size, float scale, float* pm, float* pl, float* pa,
+                    int64_t partial_slots, void* stream);
+
+/* ---- kernel 3: chunked-prefill paged attention ---------------------------------------------
+ * replaces: engine/src/attn_cute.h:7-12 LaunchAttnPrefillCute (engine/src/attn_cute.cu:30-163).
+ * For prefill request r = rids[z], z < R: rows qstart[r] .. qstart[r]+qlen[r]-1 are contiguous,
+ * row i attends key positions <= pos[qstart[r]+i] through bt + r*max_blocks; output layout as
+ * for decode. max_qlen bounds qlen over the R requests. R <= 0 is a no-op. */
+int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
+                     int n_heads, int n_kv, int head_dim, const int32_t* pos,
+                     const int32_t* qstart, const int32_t* qlen, const int32_t* rids, int R,
+                     int max_qlen, const int32_t* bt, int max_blocks, int block_size, float scale,
+                     void* stream);
+
+/* ---- kernel 4: prefix-cache block copy (copy-on-write) and gather --------------------------
+ * No reference kernel exists: the reference shares only full blocks by aliasing block-table
+ * entries (engine/src/scheduler.cc:27-44) and so never copies. These operators add copy-on-write
+ * for a partially filled shared tail block and a contiguous export of a block list.
+ * copy:   cache[pairs[2i+1]] <- cache[pairs[2i]] (whole page, both planes). Destinations must be
+ *         distinct from each other and from every source.
+ * gather: out[i] <- cache[list[i]], out is [n][2][16][row_elems].
+ * scatter: the inverse of gather, cache[list[i]] <- in[i]. */
+int fqb_copy_blocks(void* cache, int num_blocks, int kv_heads_local, const int32_t* pairs,
+                    int n_pairs, void* stream);
+int fqb_copy_blocks_layers(void* const* layer_caches /* device array of n_layers pointers */,
+                           int n_layers, int num_blocks, int kv_heads_local, const int32_t* pairs,
+                           int n_pairs, void* stream);
+int fqb_gather_blocks(const void* cache, int num_blocks, int kv_heads_local, const int32_t* list,
+                      int n, void* out, void* stream);
+int fqb_scatter_blocks(void* cache, int num_blocks, int kv_heads_local, const int32_t* list, int n,
+                       const void* in, void* stream);
+
+/* ---- device status --------------------------------------------------------------------------
+ * The kernels never trap and never wait without a limit. A bounded wait that runs out, or an
+ * index outside its range, is recorded in a status word in the library's own device memory and
+ * the kernel carries on without touching memory it should not. fqb_device_status() copies the
+ * word back (it synchronises the device: call it at the step boundary, where the reference
+ * checks its own CUDA errors, engine/src/model_runtime.cu:309) and returns FQB_OK,
+ * FQB_ERR_TIMEOUT or FQB_ERR_INDEX; detail[0..3] (host, optional) receives
+ * {code, kernel id, block index, value}. fqb_device_status_reset() clears it. */
+int fqb_device_status(int32_t* detail /* host, may be NULL */);
+int fqb_device_status_reset(void);
+
+/* ---- host side: block allocator with prefix cache (no CUDA) ---------------------------------
+ * replaces: engine/src/block_allocator.h:21-101 (class BlockAllocator) and the prefix functions
+ * of engine/src/scheduler.cc:16-57. One handle = one pool of block ids [0, num_blocks);
+ * not thread-safe, like the reference (one engine thread). */
+typedef struct fqb_alloc fqb_alloc;
+
+fqb_alloc* fqb_alloc_create(int num_blocks);
+void fqb_alloc_destroy(fqb_alloc* a);
+int fqb_alloc_num_blocks(const fqb_alloc* a);
+int fqb_alloc_num_free(const fqb_alloc* a);                  /* BlockAllocator::NumFree  */
+int fqb_alloc_blocks_for(int n_tokens);                      /* BlockAllocator::BlocksFor */
+int fqb_alloc_refcount(const fqb_alloc* a, int block);
+uint64_t fqb_alloc_block_hash(const fqb_alloc* a, int block);
+int fqb_alloc_one(fqb_alloc* a);                             /* AllocOne: id or FQB_ERR_NOMEM */
+int fqb_alloc_free_one(fqb_alloc* a, int block);             /* FreeOne                    */
+int fqb_alloc_free_table(fqb_alloc* a, int32_t* table, int* len); /* Free: frees all, *len=0 */
+/* Grow: extend table (*len entries, room for cap) to cover n_tokens. FQB_ERR_NOMEM when the pool
+ * runs dry; the blocks obtained so far stay in the table (the caller preempts and retries). */
+int fqb_alloc_grow(fqb_alloc* a, int32_t* table, int* len, int cap, int n_tokens);
+int fqb_alloc_cache_lookup(fqb_alloc* a, uint64_t hash);     /* CacheLookup: id or -1 (miss) */
+int fqb_alloc_cache_insert(fqb_alloc* a, int block, uint64_t hash); /* CacheInsert          */
+
+/* replaces: engine/src/scheduler.cc:16-24 HashBlock */
+uint64_t fqb_hash_block(uint64_t parent, const int32_t* tokens, int n);
+/* replaces: engine/src/scheduler.cc:27-44 AcquirePrefix (+ Request::AdoptPrefix,
+ * engine/src/scheduler.h:54-58). Returns the number of blocks adopted into table[0..); the
+ * request's computed-token count becomes that * 16. *last_hash receives the chain hash. */
+int fqb_acquire_prefix(fqb_alloc* a, const int32_t* tokens, int n_tokens, int32_t* table, int cap,
+                       uint64_t* last_hash);
+/* replaces: engine/src/scheduler.cc:46-57 CacheBlocks. Returns the new cached-block count. */
+int fqb_cache_blocks(fqb_alloc* a, const int32_t* tokens, int computed, const int32_t* table,
+                     int cached_blocks, uint64_t* last_hash);
+/* Copy-on-write decision before writing token position pos of a sequence: when the target block
+ * is shared (refcount > 1) and the write does not start the block, a private block replaces it in
+ * the table and pair[0..1] = {shared, private} must be copied (fqb_copy_blocks) before the append.
+ * Returns 1 (pair produced), 0 (nothing to do) or FQB_ERR_NOMEM. */
+int fqb_cow_prepare(fqb_alloc* a, int32_t* table, int pos, int32_t* pair);
+
+/* ---- host side: step metadata ----------------------------------------------------------------
+ * replaces: engine/src/model_runtime.cu:54-91 (PackBlockTables, SplitDecodePrefill). All host
+ * pointers. counts = {n_decode, n_prefill, prefill_max_qlen}. tables[r] / table_len[r] are the
+ * requests' block tables, packed into bt_out with row stride bt_stride (tail left untouched). */
+int fqb_step_pack(const int32_t* req_index, int n_rows, int n_req, const int32_t* const* tables,
+                  const int32_t* table_len, int bt_stride, int32_t* bt_out, int32_t* qstart,
+                  int32_t* qlen, int32_t* decode_rids, int32_t* prefill_rids, int32_t* counts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FQB_H_ */
