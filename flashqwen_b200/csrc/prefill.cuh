@@ -162,6 +162,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) 
       report(FQB_ERR_TIMEOUT, kKidPrefill, kt);
     }
     if (kt * kTok <= wmax) {  // some row of this warp sees the page
+      if (kt == ntiles - 1 && last_pos - kt * kTok + 1 < kTok) {
+        // token slots past the chunk's last position were never written: their V rows may hold
+        // anything (0 * NaN would poison PV). Every warp clears them before its own reads;
+        // the warps store the same zeros, so the overlap is harmless.
+        uint8_t* st = smem + slot * kPageBytes;
+        if (lane < 16)
+          for (int row = last_pos - kt * kTok + 1; row < kTok; ++row)
+            *reinterpret_cast<uint4*>(st + kPlaneBytes + (lane >> 3) * kHalfBytes + row * 128 +
+                                      ((lane & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        __syncwarp();
+      }
       const uint32_t kbase = smem_u32(smem + slot * kPageBytes), vbase = kbase + kPlaneBytes;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll

@@ -1,0 +1,158 @@
+"""fqb_attn_decode (kernel 2) through the C ABI against the oracle. Tolerance: max-abs <= 2e-2."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flashqwen_b200 as fq
+import oracle_lib as O
+from flashqwen_b200 import synth
+from golden import cases
+from gpu_util import DEV, TOL, Scratch, dv, host, maxabs, run_decode
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def oracle_decode(c, **kw):
+    return O.attn_decode(c.qkv, c.q_stride, c.cache, c.n_heads, c.n_kv, c.pos, c.qstart, c.decode_rids, c.bt,
+                         c.scale, rows=len(c.pos), **kw)
+
+
+@pytest.fixture(autouse=True)
+def _clean_status():
+    fq.device_status_reset()
+    yield
+
+
+def test_config1_matches_oracle_and_reference_fixture():
+    c = cases.decode_config1()
+    got = run_decode(c)
+    assert maxabs(got, oracle_decode(c)) <= TOL
+    path = os.path.join(GOLD, "ref_gpu_vectors.npz")
+    if os.path.exists(path):
+        assert maxabs(got, np.load(path)["decode_config1_out"]) <= TOL
+
+
+@pytest.mark.parametrize("length", [1, 2, 15, 16, 17, 31, 32, 33, 47, 48, 49, 127, 128, 129, 255, 256, 257, 1000])
+def test_single_sequence_lengths(length):
+    c = synth.decode_case([length], 80, seed=length, n_kv=2)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
+@pytest.mark.parametrize("n_kv", [1, 2, 4, 8])
+def test_ragged_batch_every_head_count(n_kv):
+    lengths = [1, 15, 16, 17, 31, 33, 100, 257, 640, 5, 1024, 2]
+    c = synth.decode_case(lengths, 160, seed=10 + n_kv, n_kv=n_kv, shuffle_rids=True)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
+def test_long_context_is_split_over_many_ctas_and_combined():
+    c = synth.decode_case([20000, 3], 1400, seed=21, n_kv=1)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
+def test_batch_above_one_launch_capacity():
+    rng = np.random.default_rng(5)
+    lengths = rng.integers(1, 40, size=600).tolist()
+    c = synth.decode_case(lengths, 2000, seed=22, n_kv=1)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
+def test_decode_rows_inside_a_mixed_step():
+    # decode requests are a subset of the requests: rows of prefill requests must stay untouched
+    c = synth.decode_case([100, 7, 300, 64, 33], 64, seed=23, n_kv=2)
+    c.decode_rids = np.asarray([3, 0, 4], np.int32)
+    got = run_decode(c)
+    want = oracle_decode(c)
+    for r in (0, 3, 4):
+        assert maxabs(got[r], want[r]) <= TOL
+    for r in (1, 2):
+        assert (got[r] == 0x7FC0).all()
+
+
+def test_sequence_without_keys_gives_zeros():
+    c = synth.decode_case([5, 9], 8, seed=24, n_kv=1)
+    c.pos[0] = -1
+    got = run_decode(c)
+    assert (got[0] == 0).all() and maxabs(got[1], oracle_decode(c)[1]) <= TOL
+
+
+def test_scratch_contents_do_not_matter_between_calls():
+    c = synth.decode_case([700, 900, 50], 128, seed=25, n_kv=2)
+    s = Scratch(3, c.n_heads, c.max_blocks)
+    a = run_decode(c, scratch=s)
+    s.pa.fill_(float("inf"))
+    b = run_decode(c, scratch=s)
+    assert np.array_equal(a, b)
+
+
+def test_reference_sized_scratch_is_enough():
+    # the engine gives slots*64*16 floats (engine/src/kernels.cuh:33-37)
+    c = synth.decode_case([4000] * 4, 1100, seed=26, n_kv=8)
+    s = Scratch(4, c.n_heads, c.max_blocks, slots=4 * 64 * 16)
+    assert maxabs(run_decode(c, scratch=s), oracle_decode(c)) <= TOL
+
+
+def test_too_small_scratch_is_refused_before_launch():
+    c = synth.decode_case([100], 8, seed=27, n_kv=1)
+    s = Scratch(1, c.n_heads, c.max_blocks, slots=64)
+    with pytest.raises(fq.FqbError) as e:
+        run_decode(c, scratch=s)
+    assert e.value.code == -4
+
+
+def test_head_sharded_outputs_concatenate_to_the_full_result():
+    c = synth.decode_case([333, 48, 1025], 128, seed=28, n_kv=8)
+    full = oracle_decode(c).reshape(3, 32, 128)
+    for world in (2, 4, 8):
+        kvl = 8 // world
+        for rank in range(world):
+            sl = slice(rank * kvl * 128, (rank + 1) * kvl * 128)
+            local_cache = np.ascontiguousarray(c.cache[..., sl])
+            got = run_decode(c, cache=dv(local_cache), head_begin=rank * kvl, n_kv=kvl).reshape(3, kvl * 4, 128)
+            assert maxabs(got, full[:, rank * kvl * 4:(rank + 1) * kvl * 4]) <= TOL
+
+
+def test_out_of_range_block_id_is_reported_not_followed():
+    c = synth.decode_case([40], 8, seed=29, n_kv=1)
+    c.bt[0, 1] = 12345
+    run_decode(c, check_status=False)
+    code, detail = fq.device_status(raise_on_error=False)
+    assert code == -6 and detail[1] == 2 and detail[3] == 12345
+    fq.device_status_reset()
+    assert fq.device_status()[0] == 0
+
+
+def test_linearity_in_v_at_config2_size():
+    """Size-independent property at the full batch-64 shape: scaling V by 2 scales the output by 2
+    exactly (power of two), and permuting physical blocks leaves it unchanged."""
+    lengths = synth.config2_lengths(seed=0)
+    nb = sum((L + 15) // 16 for L in lengths) + 7
+    g = torch.Generator(device=DEV).manual_seed(0)
+    cache = torch.randn((nb, 2, 16, 1024), generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    rng = np.random.default_rng(0)
+    tables = synth.assign_blocks(lengths, nb, rng)
+    c = synth.Case(n_heads=32, n_kv=8, num_blocks=nb, max_blocks=256, bt=synth.pack_tables(tables, 256),
+                   pos=np.asarray([L - 1 for L in lengths], np.int32), qstart=np.arange(64, dtype=np.int32),
+                   decode_rids=np.arange(64, dtype=np.int32), q_stride=6144, scale=128 ** -0.5,
+                   qkv=synth.f32_to_bf16(rng.standard_normal((64, 6144), dtype=np.float32)))
+    base = run_decode(c, cache=cache.view(torch.int16))
+    assert np.isfinite(synth.bf16_to_f32(base)).all()
+    cache2 = cache.clone()
+    cache2[:, 1] *= 2
+    doubled = run_decode(c, cache=cache2.view(torch.int16))
+    assert np.array_equal(synth.bf16_to_f32(doubled), 2 * synth.bf16_to_f32(base))
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(1))
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(nb)
+    cache3 = cache[perm.to(DEV)].contiguous()           # block b now lives at inv[b]
+    c3 = synth.Case(dict(c))
+    c3.bt = inv.numpy().astype(np.int32)[c.bt]
+    assert np.array_equal(run_decode(c3, cache=cache3.view(torch.int16)), base)
+    # spot-check 3 sequences against the oracle on the host copy
+    hc = host(cache.view(torch.int16))
+    pick = np.asarray([int(np.argmin(lengths)), int(np.argmax(lengths)), 17], np.int32)
+    want = O.attn_decode(c.qkv, 6144, hc, 32, 8, c.pos, c.qstart, pick, c.bt, c.scale, rows=64)
+    assert maxabs(base[pick], want[pick]) <= TOL

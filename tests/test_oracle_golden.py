@@ -136,9 +136,11 @@ def test_decode_matches_reference_kernels_ragged():
 def test_norm_rope_append_prefill_match_reference_kernels():
     g = _gpu_fixture()
     c = cases.prefill_small()
-    cos, sin = O.rope_tables(int(c.pos.max()) + 1)
-    scos, ssin = synth.rope_tables(int(c.pos.max()) + 1)
-    assert np.array_equal(cos, scos) and np.array_equal(sin, ssin)
+    # the fixture was made with the numpy tables, so the oracle gets the same ones; the oracle's own
+    # table builder (C++ powf/cosf, as the engine does) agrees with them to fp32 angle precision
+    cos, sin = synth.rope_tables(int(c.pos.max()) + 1)
+    ocos, osin = O.rope_tables(int(c.pos.max()) + 1)
+    assert np.max(np.abs(cos - ocos)) < 1e-4 and np.max(np.abs(sin - osin)) < 1e-4
     qkv = c.qkv_raw.copy()
     O.head_norm_rope(qkv, c.wq, c.wk, cos, sin, c.pos, c.n_heads, c.n_kv, c.q_stride)
     ref_qkv = g["prefill_qkv_after"]
