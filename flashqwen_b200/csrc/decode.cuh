@@ -1,30 +1,33 @@
-// Kernel 2: GQA-shared split-K paged decode attention and its log-sum-exp combine.
+// Kernel 2: GQA-shared split-K paged decode attention with the log-sum-exp combine fused in.
 //
 // Operator semantics follow the reference's LaunchAttnDecodeCute
 // (engine/src/attn_cute.cu:165-261 of the FlashQwen tree): decode sequence di attends keys
 // 0..qpos inclusive, one kv head serves its 4 query heads, fp32 accumulation, bf16 output at
 // out[(flat*n_heads + h)*128 + d]. The design is not the reference's:
 //
-//   * Work is the flat list of page slices (sequence, kv head, page), each 8 KiB (K and V rows of
-//     one head of one 16-token page). The list is cut into equal contiguous ranges, one per
-//     persistent CTA, on the device from the actual context lengths -- the grid depends only on
-//     the SM count, so the launch can sit in a CUDA graph while lengths change.
-//   * Each warp owns a private ring of NS page buffers in shared memory filled by single-thread
-//     TMA tensor loads (5-D box, 128-byte swizzle) that complete on the ring's mbarriers; the
-//     warp that consumes a buffer refills it, so there is no cross-warp handshake in the stream
-//     and loads run ahead across (sequence, head) boundaries.
+//   * Work is the flat list of pages of all sequences (sequence-major). It is cut into equal
+//     contiguous page ranges, one per persistent CTA, on the device from the actual context
+//     lengths -- the grid depends only on the SM count, so the launch can sit in a CUDA graph
+//     while lengths change. A CTA handles every local kv head of its pages: warp w serves head
+//     w % HEADS, so the loads a CTA has in flight cover whole 64 KiB pages (all heads of K and V
+//     are adjacent in memory), not isolated 256-byte rows.
+//   * Each warp owns a private ring of NS page buffers (8 KiB: K and V rows of one head of one
+//     16-token page) filled by single-thread TMA tensor loads (5-D box, 128-byte swizzle) that
+//     complete on the ring's mbarriers. The warp that consumes a buffer refills it, so the stream
+//     has no cross-warp handshake and runs ahead across sequence boundaries. With all 8 kv heads
+//     local (HEADS == NW) a warp never synchronises with another warp at all.
 //   * Scores and PV products use mma.sync m16n8k16 with the 4 query heads as rows 0..3 of the
 //     16-row A tile (rows 4..15 are zero padding): S[4x16] = Q[4x128] K^T, O[4x128] += P[4x16] V.
+//     The query rows of the next sequence are fetched into registers while the current one runs.
 //   * A (sequence, head) pair that lies inside one CTA is normalised and written straight to
-//     `out`; a pair cut by a CTA boundary leaves one unnormalised partial per CTA
-//     (slot = pair index + CTA index) and the combine kernel merges them.
+//     `out`. A pair cut by CTA boundaries leaves one unnormalised partial per CTA and takes a
+//     ticket on the pair's arrival counter; the warp that takes the last ticket merges the
+//     partials (log-sum-exp) and writes `out` -- no second kernel, no inter-CTA waiting.
 #pragma once
 
 #include "common.cuh"
 
 namespace fqb {
-
-constexpr int kMinSlicesPerCta = 16;
 
 struct DecodeParams {
   const __nv_bfloat16* q;
@@ -42,28 +45,43 @@ struct DecodeParams {
   float* pl;
   float* pa;
   long long partial_slots;
+  unsigned epoch;  // differs from launch to launch, never 0
+  int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
 };
 
-// Tail of pm / pl reused as integers to hand the partition to the combine kernel:
-//   pm_i[slots-1] = slices per CTA (W); pm_i[slots-2-di] = first page index of sequence di in the
-//   flat list (exclusive prefix sum of pages); pl_i[slots-2-di] = pages of sequence di.
-__device__ __forceinline__ int* meta_w(const DecodeParams& P) {
-  return reinterpret_cast<int*>(P.pm) + (P.partial_slots - 1);
+// Scratch layout. Partial (sequence di, CTA b, kv head, q head g) lives at slot
+// ((di + b) * n_kv + kvh) * 4 + g of pm / pl / pa: along the flat page list the cuts are sequence
+// boundaries and CTA boundaries, so di + b numbers the segments uniquely. The arrival counters
+// (one 64-bit word per (sequence, kv head)) sit at the end of pl.
+__host__ __device__ inline long long decode_counter_base(long long partial_slots, int n_pairs) {
+  return (partial_slots - 2LL * n_pairs) & ~1LL;  // float index into pl, 8-byte aligned
 }
-__device__ __forceinline__ int* meta_cum(const DecodeParams& P, int di) {
-  return reinterpret_cast<int*>(P.pm) + (P.partial_slots - 2 - di);
-}
-__device__ __forceinline__ int* meta_np(const DecodeParams& P, int di) {
-  return reinterpret_cast<int*>(P.pl) + (P.partial_slots - 2 - di);
+__host__ __device__ inline long long decode_slots_needed(int n_decode, int n_kv, int grid) {
+  return (static_cast<long long>(n_decode) + grid) * n_kv * kGroup + 2LL * n_decode * n_kv + 2;
 }
 
-// MAXD = sequences per launch (the host loops over larger batches)
+// Takes a ticket on an arrival counter {epoch : 32 | count : 32}. A word whose epoch field is not
+// this launch's (stale or never initialised memory) counts as empty, so the scratch needs no
+// clearing; the caller that gets the last ticket clears the word for a replay with the same epoch.
+__device__ __forceinline__ bool take_ticket_is_last(unsigned long long* c, unsigned epoch, int total) {
+  unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(c);
+  unsigned cnt = 0;
+  for (int tries = 0; tries < 4096; ++tries) {
+    cnt = (static_cast<unsigned>(seen >> 32) == epoch) ? static_cast<unsigned>(seen) + 1u : 1u;
+    const unsigned long long want = (static_cast<unsigned long long>(epoch) << 32) | cnt;
+    const unsigned long long old = atomicCAS(c, seen, want);
+    if (old == seen) return cnt == static_cast<unsigned>(total);
+    seen = old;
+  }
+  report(FQB_ERR_TIMEOUT, kKidCombine, total);
+  return false;
+}
+
 template <int NW, int NS, int MAXD>
 struct DecodeSmem {
   static constexpr int kStageBytes = NW * NS * kPageBytes;
   static constexpr int kBarOff = kStageBytes;
-  static constexpr int kQOff = kBarOff + NW * NS * 8;
-  static constexpr int kMoOff = kQOff + 2 * kGroup * kHd * 2;
+  static constexpr int kMoOff = kBarOff + NW * NS * 8;
   static constexpr int kMmOff = kMoOff + NW * kGroup * kHd * 4;
   static constexpr int kMlOff = kMmOff + NW * kGroup * 4;
   static constexpr int kROff = kMlOff + NW * kGroup * 4;
@@ -74,41 +92,72 @@ struct DecodeSmem {
   static constexpr int kAlloc = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
-// Walks the items (maximal runs of pages of one (sequence, kv head) pair) of a CTA's range.
+// An item is a maximal run of pages of one sequence inside a CTA's page range.
 struct ItemCursor {
-  int off;     // flat slice offset of the current item's first page; >= hi when exhausted
-  int di, kvh;
-  int pb, pe;  // page range [pb, pe) of the item
+  int off;     // flat page offset of the item's first page; >= hi when exhausted
+  int di;
+  int pb, pe;  // page range [pb, pe) inside the sequence
   int np;      // pages of the whole sequence
 };
 
-__device__ __forceinline__ void item_at(ItemCursor& c, int off, int hi, int n_decode, int n_kv,
-                                        const int* s_cum, const int* s_qpos) {
+__device__ __forceinline__ void item_at(ItemCursor& c, int off, int hi, int n_decode, const int* s_cum) {
   c.off = off;
   if (off >= hi) return;
-  // largest di with s_cum[di] * n_kv <= off (s_cum[n_decode] * n_kv = total > off)
-  int lo = 0, up = n_decode;
+  int lo = 0, up = n_decode;  // largest di with s_cum[di] <= off (s_cum[n_decode] = total > off)
   while (up - lo > 1) {
-    int mid = (lo + up) >> 1;
-    if (s_cum[mid] * n_kv <= off) lo = mid; else up = mid;
+    const int mid = (lo + up) >> 1;
+    if (s_cum[mid] <= off) lo = mid; else up = mid;
   }
   c.di = lo;
-  c.np = s_qpos[lo] / kTok + 1;
-  int rem = off - s_cum[lo] * n_kv;
-  c.kvh = rem / c.np;
-  c.pb = rem - c.kvh * c.np;
+  c.np = s_cum[lo + 1] - s_cum[lo];
+  c.pb = off - s_cum[lo];
   c.pe = min(c.np, c.pb + (hi - off));
 }
 
-template <int NW, int NS, int MINB, int MAXD>
+// Merges the partials of pair (di, kvh) left by CTAs b0..b1 and writes the 4 query heads' rows.
+// One warp: lane -> q head g = lane / 8 and dims (lane % 8) * 4 + 32 * i, i < 4.
+__device__ __forceinline__ void merge_pair(const DecodeParams& P, int di, int kvh, int b0, int b1, int flat,
+                                           int lane) {
+  const int g = lane >> 3, dbase = (lane & 7) * 4;
+  float gm = kNegBig;
+  for (int b = b0; b <= b1; ++b)
+    gm = fmaxf(gm, __ldcg(P.pm + ((static_cast<long long>(di) + b) * P.n_kv + kvh) * kGroup + g));
+  float gl = 0.f;
+  float4 acc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int b = b0; b <= b1; ++b) {
+    const long long slot = ((static_cast<long long>(di) + b) * P.n_kv + kvh) * kGroup + g;
+    const float c = fast_exp2(__ldcg(P.pm + slot) - gm);
+    gl += __ldcg(P.pl + slot) * c;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(P.pa + slot * kHd + dbase + 32 * i));
+      acc[i].x += v.x * c; acc[i].y += v.y * c; acc[i].z += v.z * c; acc[i].w += v.w * c;
+    }
+  }
+  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  __nv_bfloat16* o = P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd + dbase;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint2 pk;
+    pk.x = pack_bf16(acc[i].x * inv, acc[i].y * inv);
+    pk.y = pack_bf16(acc[i].z * inv, acc[i].w * inv);
+    *reinterpret_cast<uint2*>(o + 32 * i) = pk;
+  }
+}
+
+// HEADS = local kv heads (1, 2, 4 or 8); SUB = NW / HEADS warps share one head's pages.
+template <int NW, int NS, int HEADS, int MINB, int MAXD>
 __global__ void __launch_bounds__(NW * 32, MINB)
-decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
+decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   using L = DecodeSmem<NW, NS, MAXD>;
+  constexpr int SUB = NW / HEADS;
+  static_assert(NW % HEADS == 0, "warps must divide evenly over the heads");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + L::kQOff);
   float* s_mo = reinterpret_cast<float*>(smem + L::kMoOff);
   float* s_mm = reinterpret_cast<float*>(smem + L::kMmOff);
   float* s_ml = reinterpret_cast<float*>(smem + L::kMlOff);
@@ -118,7 +167,8 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
   int* s_cum = reinterpret_cast<int*>(smem + L::kCumOff);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_decode = P.n_decode, n_kv = P.n_kv;
+  const int n_decode = P.n_decode;
+  const int kvh = P.kvh_base + warp % HEADS, sub = warp / HEADS;
 
   if (tid == 0) {
     tma_prefetch_desc(&tmap);
@@ -127,14 +177,20 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
   }
   // ---- per-sequence metadata (3 dependent loads) and the page prefix sum ----
   for (int di = tid; di < n_decode; di += NW * 32) {
-    int r = P.rids[di];
-    int flat = P.qstart[r];
+    const int r = P.rids[di];
+    const int flat = P.qstart[r];
     int qp = P.pos[flat];
     if (qp >= P.max_blocks * kTok) {
       report(FQB_ERR_INDEX, kKidDecode, qp);
       qp = P.max_blocks * kTok - 1;
     }
-    if (qp < -1) qp = -1;
+    if (qp < 0) {
+      qp = -1;
+      if (blockIdx.x == 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
+        uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(flat) * P.n_heads * kHd);
+        for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
     s_r[di] = r;
     s_flat[di] = flat;
     s_qpos[di] = qp;
@@ -144,41 +200,36 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     constexpr int kPer = MAXD / 32;
     int sum = 0;
     for (int i = 0; i < kPer; ++i) {
-      int idx = lane * kPer + i;
+      const int idx = lane * kPer + i;
       if (idx < n_decode) sum += (s_qpos[idx] + kTok) / kTok;  // qpos/16+1, 0 when qpos = -1
     }
     int incl = sum;
     for (int o = 1; o < 32; o <<= 1) {
-      int y = __shfl_up_sync(0xffffffffu, incl, o);
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += y;
     }
     int run = incl - sum;
     for (int i = 0; i < kPer; ++i) {
-      int idx = lane * kPer + i;
+      const int idx = lane * kPer + i;
       if (idx < n_decode) {
         s_cum[idx] = run;
         run += (s_qpos[idx] + kTok) / kTok;
       }
     }
-    int total = __shfl_sync(0xffffffffu, incl, 31);
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
     if (lane == 0) s_cum[n_decode] = total;
   }
   __syncthreads();
 
-  const int total_slices = s_cum[n_decode] * n_kv;
+  const int total_pages = s_cum[n_decode];
   const int nb = static_cast<int>(gridDim.x);
-  const int W = max(kMinSlicesPerCta, (total_slices + nb - 1) / nb);
-  if (blockIdx.x == 0) {
-    for (int di = tid; di < n_decode; di += NW * 32) {
-      *meta_cum(P, di) = s_cum[di];
-      *meta_np(P, di) = (s_qpos[di] + kTok) / kTok;
-    }
-    if (tid == 0) *meta_w(P) = W;
-  }
+  const int W = max(2 * SUB, (total_pages + nb - 1) / nb);  // pages per CTA
   const long long lo_ll = static_cast<long long>(blockIdx.x) * W;
-  if (lo_ll >= total_slices) return;  // whole CTA leaves together; nothing in flight
+  if (lo_ll >= total_pages) return;  // whole CTA leaves together; nothing in flight
   const int lo = static_cast<int>(lo_ll);
-  const int hi = min(total_slices, lo + W);
+  const int hi = min(total_pages, lo + W);
+  unsigned long long* counters =
+      reinterpret_cast<unsigned long long*>(P.pl + decode_counter_base(P.partial_slots, n_decode * P.n_kv));
 
   uint8_t* my_stage = smem + warp * NS * kPageBytes;
   uint64_t* my_bar = bars + warp * NS;
@@ -186,14 +237,14 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
 
   // ---- producer cursor: next page this warp will request ----
   ItemCursor pc;
-  item_at(pc, lo, hi, n_decode, n_kv, s_cum, s_qpos);
-  int p_page = pc.pb + warp;
+  item_at(pc, lo, hi, n_decode, s_cum);
+  int p_page = pc.pb + sub;
   int p_blk = 0;
   int islot = 0;
   auto prod_settle = [&]() {  // move to the next item until this warp has a page in it
     while (pc.off < hi && p_page >= pc.pe) {
-      item_at(pc, pc.off + (pc.pe - pc.pb), hi, n_decode, n_kv, s_cum, s_qpos);
-      p_page = pc.pb + warp;
+      item_at(pc, pc.off + (pc.pe - pc.pb), hi, n_decode, s_cum);
+      p_page = pc.pb + sub;
     }
     if (pc.off < hi)
       p_blk = __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page);
@@ -204,11 +255,10 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
       report(FQB_ERR_INDEX, kKidDecode, p_blk);  // the load below then reads zeros
     if (lane == 0) {
       mbar_expect_tx(&my_bar[islot], kPageBytes);
-      tma_load_page(my_stage + islot * kPageBytes, &tmap, &my_bar[islot], 0, 0, pc.kvh * 2, 0,
-                    p_blk);
+      tma_load_page(my_stage + islot * kPageBytes, &tmap, &my_bar[islot], 0, 0, kvh * 2, 0, p_blk);
     }
     islot = (islot + 1 == NS) ? 0 : islot + 1;
-    p_page += NW;
+    p_page += SUB;
     prod_settle();
   };
   prod_settle();
@@ -216,43 +266,35 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
   for (int s = 0; s < NS; ++s) prod_issue();
 
   // ---- consumer ----
-  ItemCursor cc;
-  item_at(cc, lo, hi, n_decode, n_kv, s_cum, s_qpos);
-  int cslot = 0;
-  uint32_t cphase = 0;
-  int qbuf = 0;
-  // q rows of the first item: 4 heads x 128 bf16 = 64 chunks of 16 bytes
-  if (tid < 64)
-    cp_async16(sQ + tid * 8, P.q + static_cast<long long>(s_flat[cc.di]) * P.q_stride +
-                                 cc.kvh * (kGroup * kHd) + tid * 8);
-  cp_async_commit();
-
   const int g = lane >> 2, t = lane & 3;
   const int mat = lane >> 3;
   const int k_tok = ((mat >> 1) << 3) + (lane & 7), k_sel = mat & 1;
   const int v_tok = ((mat & 1) << 3) + (lane & 7), v_sel = mat >> 1;
+  // A-fragment words of this lane inside the 4 x 128 q block of a kv head (rows g >= 4 are padding)
+  auto load_q = [&](uint32_t (&dst)[8][2], int di) {
+    const uint32_t* qw = reinterpret_cast<const uint32_t*>(
+        P.q + static_cast<long long>(s_flat[di]) * P.q_stride + kvh * (kGroup * kHd) + (g & 3) * kHd);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint32_t a = __ldg(qw + ks * 8 + t), b = __ldg(qw + ks * 8 + t + 4);
+      dst[ks][0] = g < kGroup ? a : 0u;
+      dst[ks][1] = g < kGroup ? b : 0u;
+    }
+  };
+
+  ItemCursor cc;
+  item_at(cc, lo, hi, n_decode, s_cum);
+  int cslot = 0;
+  uint32_t cphase = 0;
+  uint32_t qa[8][2], qn[8][2];
+  load_q(qa, cc.di);
 
 #pragma unroll 1
   while (cc.off < hi) {
-    cp_async_wait_all();
-    __syncthreads();  // q of this item visible; merge buffers of the previous item free
     ItemCursor nx;
-    item_at(nx, cc.off + (cc.pe - cc.pb), hi, n_decode, n_kv, s_cum, s_qpos);
-    if (nx.off < hi && tid < 64)
-      cp_async16(sQ + (qbuf ^ 1) * (kGroup * kHd) + tid * 8,
-                 P.q + static_cast<long long>(s_flat[nx.di]) * P.q_stride +
-                     nx.kvh * (kGroup * kHd) + tid * 8);
-    cp_async_commit();
+    item_at(nx, cc.off + (cc.pe - cc.pb), hi, n_decode, s_cum);
+    if (nx.off < hi) load_q(qn, nx.di);  // lands while this item is processed
 
-    uint32_t qa[8][2];
-    {
-      const uint32_t* qw = reinterpret_cast<const uint32_t*>(sQ + qbuf * (kGroup * kHd));
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        qa[ks][0] = g < kGroup ? qw[(g * kHd + ks * 16 + 2 * t) >> 1] : 0u;
-        qa[ks][1] = g < kGroup ? qw[(g * kHd + ks * 16 + 2 * t + 8) >> 1] : 0u;
-      }
-    }
     float o[16][4];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -260,7 +302,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     const int qpos = s_qpos[cc.di];
 
 #pragma unroll 1
-    for (int page = cc.pb + warp; page < cc.pe; page += NW) {
+    for (int page = cc.pb + sub; page < cc.pe; page += SUB) {
       if (!dead && !mbar_wait_bounded(&my_bar[cslot], cphase)) {
         dead = true;
         report(FQB_ERR_TIMEOUT, kKidDecode, page);
@@ -321,94 +363,115 @@ decode_split_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
       prod_issue();
     }
 
-    // ---- merge the warps' partial softmax states of this item ----
+    // ---- end of item: this warp's softmax state of (cc.di, kvh) over its pages ----
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (g < kGroup) {
-      float* dst = s_mo + (warp * kGroup + g) * kHd + 2 * t;
+    const bool whole = cc.pb == 0 && cc.pe == cc.np;
+    const int flat = s_flat[cc.di];
+    const int b0 = s_cum[cc.di] / W, b1 = (s_cum[cc.di] + cc.np - 1) / W;  // CTAs that see this sequence
+    unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
+    const long long slot0 = ((static_cast<long long>(cc.di) + blockIdx.x) * P.n_kv + kvh) * kGroup;
+
+    if (SUB == 1) {
+      // the warp is the only one on this head: straight from registers, no block barrier
+      if (whole) {
+        if (g < kGroup) {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          uint32_t* dst = reinterpret_cast<uint32_t*>(
+              P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
-      if (t == 0) {
-        s_mm[warp * kGroup + g] = m;
-        s_ml[warp * kGroup + g] = l;
-      }
-    }
-    __syncthreads();
-    if (tid < kGroup * 32) {
-      const int h = tid >> 5, d4 = (tid & 31) * 4;
-      float gm = kNegBig;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) gm = fmaxf(gm, s_mm[w * kGroup + h]);
-      float gl = 0.f;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        const float c = fast_exp2(s_mm[w * kGroup + h] - gm);
-        gl += s_ml[w * kGroup + h] * c;
-        const float4 v = *reinterpret_cast<const float4*>(s_mo + (w * kGroup + h) * kHd + d4);
-        acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
-      }
-      const int head = cc.kvh * kGroup + h;
-      if (cc.pb == 0 && cc.pe == cc.np) {
-        const float inv = gl > 0.f ? 1.f / gl : 0.f;
-        uint2 pk;
-        pk.x = pack_bf16(acc.x * inv, acc.y * inv);
-        pk.y = pack_bf16(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(P.out + (static_cast<long long>(s_flat[cc.di]) * P.n_heads + head) *
-                                              kHd + d4) = pk;
-      } else {
-        const long long slot =
-            (static_cast<long long>(cc.di) * n_kv + cc.kvh + blockIdx.x) * kGroup + h;
-        if ((tid & 31) == 0) {
-          P.pm[slot] = gm;
-          P.pl[slot] = gl;
+          for (int j = 0; j < 16; ++j) dst[j * 4 + t] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
         }
-        *reinterpret_cast<float4*>(P.pa + slot * kHd + d4) = acc;
+      } else {
+        if (g < kGroup) {
+          float* dst = P.pa + (slot0 + g) * kHd + 2 * t;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
+          if (t == 0) {
+            P.pm[slot0 + g] = m;
+            P.pl[slot0 + g] = l;
+          }
+          __threadfence();
+        }
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          __threadfence();
+          last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
+          __threadfence();
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
+          if (lane == 0) *ctr = 0ull;
+        }
+      }
+    } else {
+      // SUB warps hold pieces of the same head: merge them through shared memory first
+      if (g < kGroup) {
+        float* dst = s_mo + (warp * kGroup + g) * kHd + 2 * t;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
+        if (t == 0) {
+          s_mm[warp * kGroup + g] = m;
+          s_ml[warp * kGroup + g] = l;
+        }
+      }
+      __syncthreads();
+      for (int idx = tid; idx < HEADS * kGroup * 32; idx += NW * 32) {
+        const int hl = idx / (kGroup * 32), hh = P.kvh_base + hl, h = (idx >> 5) & (kGroup - 1), d4 = (idx & 31) * 4;
+        float gm = kNegBig;
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) gm = fmaxf(gm, s_mm[(s * HEADS + hl) * kGroup + h]);
+        float gl = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) {
+          const int w = s * HEADS + hl;
+          const float c = fast_exp2(s_mm[w * kGroup + h] - gm);
+          gl += s_ml[w * kGroup + h] * c;
+          const float4 v = *reinterpret_cast<const float4*>(s_mo + (w * kGroup + h) * kHd + d4);
+          acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
+        }
+        if (whole) {
+          const float inv = gl > 0.f ? 1.f / gl : 0.f;
+          uint2 pk;
+          pk.x = pack_bf16(acc.x * inv, acc.y * inv);
+          pk.y = pack_bf16(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(P.out + (static_cast<long long>(flat) * P.n_heads + hh * kGroup + h) * kHd +
+                                    d4) = pk;
+        } else {
+          const long long slot = ((static_cast<long long>(cc.di) + blockIdx.x) * P.n_kv + hh) * kGroup + h;
+          if ((idx & 31) == 0) {
+            P.pm[slot] = gm;
+            P.pl[slot] = gl;
+          }
+          *reinterpret_cast<float4*>(P.pa + slot * kHd + d4) = acc;
+          __threadfence();
+        }
+      }
+      __syncthreads();  // partials written (and the merge buffers free) before anyone takes a ticket
+      if (!whole && sub == 0) {
+        int last = 0;
+        if (lane == 0) {
+          __threadfence();
+          last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
+          __threadfence();
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
+          if (lane == 0) *ctr = 0ull;
+        }
       }
     }
     cc = nx;
-    qbuf ^= 1;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = qn[ks][0];
+      qa[ks][1] = qn[ks][1];
+    }
   }
-}
-
-// One CTA per (sequence, kv head): merges the partials of a pair that was cut by CTA boundaries
-// of the split kernel, writes zeros for a sequence without keys, and leaves pairs that the split
-// kernel finished on its own untouched. 128 threads = 4 heads x 32 lanes x 4 dims.
-__global__ void __launch_bounds__(128)
-decode_combine_kernel(const DecodeParams P) {
-  const int di = blockIdx.x / P.n_kv, kvh = blockIdx.x - di * P.n_kv;
-  const int tid = threadIdx.x, h = tid >> 5, d4 = (tid & 31) * 4;
-  const int W = *meta_w(P);
-  const int cum = *meta_cum(P, di), np = *meta_np(P, di);
-  const int head = kvh * kGroup + h;
-  if (np <= 0) {
-    const int flat = P.qstart[P.rids[di]];
-    *reinterpret_cast<uint2*>(P.out + (static_cast<long long>(flat) * P.n_heads + head) * kHd + d4) =
-        make_uint2(0u, 0u);
-    return;
-  }
-  const int start = cum * P.n_kv + kvh * np;
-  const int b0 = start / W, b1 = (start + np - 1) / W;
-  if (b0 == b1) return;
-  const long long pair = static_cast<long long>(di) * P.n_kv + kvh;
-  float gm = kNegBig;
-  for (int b = b0; b <= b1; ++b) gm = fmaxf(gm, P.pm[(pair + b) * kGroup + h]);
-  float gl = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int b = b0; b <= b1; ++b) {
-    const long long slot = (pair + b) * kGroup + h;
-    const float c = fast_exp2(P.pm[slot] - gm);
-    gl += P.pl[slot] * c;
-    const float4 v = *reinterpret_cast<const float4*>(P.pa + slot * kHd + d4);
-    acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
-  }
-  const float inv = gl > 0.f ? 1.f / gl : 0.f;
-  const int flat = P.qstart[P.rids[di]];
-  uint2 pk;
-  pk.x = pack_bf16(acc.x * inv, acc.y * inv);
-  pk.y = pack_bf16(acc.z * inv, acc.w * inv);
-  *reinterpret_cast<uint2*>(P.out + (static_cast<long long>(flat) * P.n_heads + head) * kHd + d4) = pk;
 }
 
 }  // namespace fqb

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "blocks.cuh"
@@ -121,26 +122,28 @@ int check_attn_shape(int n_heads, int n_kv, int head_dim, int block_size) {
 }
 
 // ---- decode configurations -----------------------------------------------------------------------
-// A: 8 warps x 3 page buffers, one CTA per SM (192 KiB of loads in flight per SM).
-// B: 4 warps x 3 page buffers, two CTAs per SM.
-// FQB_DECODE_CONFIG=A|B picks one at process start (tuning aid); the default is what measured best.
-struct DecodeCfgA { static constexpr int NW = 8, NS = 3, MINB = 1, MAXD = 512; };
-struct DecodeCfgB { static constexpr int NW = 4, NS = 3, MINB = 2, MAXD = 256; };
+// One launch serves HEADS local kv heads (8, 4, 2 or 1; other head counts are covered by several
+// launches). With 8 or 4 heads every warp has a head to itself (no block barrier in the stream);
+// with fewer, SUB = NW / HEADS warps share a head and merge through shared memory per sequence.
+template <int NW_, int NS_, int HEADS_, int MINB_, int MAXD_>
+struct DecodeCfg { static constexpr int NW = NW_, NS = NS_, HEADS = HEADS_, MINB = MINB_, MAXD = MAXD_; };
+using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
+using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
+using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
+using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
 
-char decode_config() {
-  static char c = 0;
-  if (!c) {
-    const char* e = std::getenv("FQB_DECODE_CONFIG");
-    c = (e && (e[0] == 'A' || e[0] == 'B')) ? e[0] : 'A';
-  }
-  return c;
+unsigned next_epoch() {
+  static std::atomic<unsigned> counter{0x5eed0000u};
+  unsigned e = ++counter;
+  while (e == 0) e = ++counter;
+  return e;
 }
 
 template <class Cfg>
 int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n_decode, int sm_count,
                   cudaStream_t st) {
   using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD>;
-  auto kern = decode_split_kernel<Cfg::NW, Cfg::NS, Cfg::MINB, Cfg::MAXD>;
+  auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
@@ -152,12 +155,12 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
   for (int base = 0; base < n_decode; base += Cfg::MAXD) {
     P.rids = rids + base;
     P.n_decode = n_decode - base < Cfg::MAXD ? n_decode - base : Cfg::MAXD;
-    const long long need = (static_cast<long long>(P.n_decode) * P.n_kv + grid) * kGroup + P.n_decode + 1;
+    const long long need = decode_slots_needed(P.n_decode, P.n_kv, grid);
     if (need > P.partial_slots)
       return set_error(FQB_ERR_WORKSPACE, "decode scratch: %lld partial slots needed, %lld given", need,
                        P.partial_slots);
+    P.epoch = next_epoch();
     kern<<<grid, Cfg::NW * 32, L::kAlloc, st>>>(map, P);
-    decode_combine_kernel<<<P.n_decode * P.n_kv, 128, 0, st>>>(P);
   }
   FQB_CUDA_TRY(cudaGetLastError());
   return FQB_OK;
@@ -220,8 +223,9 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
 int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks) {
   (void)max_blocks;  // the split count follows the SM count, not the context length
   if (max_decode <= 0 || n_heads_local <= 0) return 0;
-  // (pairs + CTAs) * 4 heads + per-sequence partition record; 2 CTAs per SM on up to 256 SMs
-  return (static_cast<int64_t>(max_decode) * (n_heads_local / kGroup) + 512) * kGroup + max_decode + 1;
+  // partials of (sequences + CTAs) segments plus the arrival counters, for one launch of at most
+  // 512 sequences on at most 512 CTAs
+  return decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512);
 }
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -234,8 +238,9 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
     return set_error(FQB_ERR_INVALID, "attn_decode: null pointer");
   if (num_blocks <= 0 || max_blocks <= 0 || partial_slots <= 0)
     return set_error(FQB_ERR_INVALID, "attn_decode: non-positive size");
-  if (!aligned16(q) || !aligned16(cache) || !aligned16(out) || !aligned16(pa) || (q_stride % 8))
-    return set_error(FQB_ERR_INVALID, "attn_decode: q, cache, out, pa and q_stride must keep 16-byte alignment");
+  if (!aligned16(q) || !aligned16(cache) || !aligned16(out) || !aligned16(pa) || (q_stride % 8) ||
+      (reinterpret_cast<uintptr_t>(pl) & 7u) || (reinterpret_cast<uintptr_t>(pm) & 3u))
+    return set_error(FQB_ERR_INVALID, "attn_decode: q, cache, out, pa and q_stride must keep 16-byte alignment, pl 8");
   DeviceInfo di;
   if (int rc = device_info(di)) return rc;
   CUtensorMap map;
@@ -259,8 +264,19 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
   P.pa = pa;
   P.partial_slots = partial_slots;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (decode_config() == 'B') return launch_decode<DecodeCfgB>(map, P, decode_rids, n_decode, di.sm_count, st);
-  return launch_decode<DecodeCfgA>(map, P, decode_rids, n_decode, di.sm_count, st);
+  // cover the local heads with launches of 8, 4, 2 or 1 heads (one launch for 8, 4, 2, 1 heads)
+  for (int base = 0; base < n_kv;) {
+    const int left = n_kv - base;
+    P.kvh_base = base;
+    int rc, took;
+    if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, st); took = 8; }
+    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, st); took = 4; }
+    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, st); took = 2; }
+    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, st); took = 1; }
+    if (rc != FQB_OK) return rc;
+    base += took;
+  }
+  return FQB_OK;
 }
 
 int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,

@@ -89,9 +89,9 @@ def test_scratch_contents_do_not_matter_between_calls():
 
 
 def test_reference_sized_scratch_is_enough():
-    # the engine gives slots*64*16 floats (engine/src/kernels.cuh:33-37)
+    # the engine gives slots*64*16 floats (engine/src/kernels.cuh:33-37), slots = 32 by default
     c = synth.decode_case([4000] * 4, 1100, seed=26, n_kv=8)
-    s = Scratch(4, c.n_heads, c.max_blocks, slots=4 * 64 * 16)
+    s = Scratch(4, c.n_heads, c.max_blocks, slots=32 * 64 * 16)
     assert maxabs(run_decode(c, scratch=s), oracle_decode(c)) <= TOL
 
 
