@@ -58,6 +58,11 @@ def parse():
     ap.add_argument("--ref-kind", default="auto", choices=["auto", "gpu", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="replay the resident step from a CUDA graph")
+    ap.add_argument("--independent", action="store_true",
+                    help="resident loop: pass FQB_DECODE_INDEPENDENT (the layers of the synthetic step are independent)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="tuning aid: run rank 0's share of an N-way kv-head shard on this one GPU")
     return ap.parse_args()
 
 
@@ -134,7 +139,7 @@ class Workload:
         self.layers, self.batch = a.layers, a.batch
         self.max_blocks = (max_ctx + PAGE - 1) // PAGE
         self.num_blocks = a.batch * self.max_blocks
-        self.kvl = N_KV if full_heads else N_KV // world
+        self.kvl = N_KV if full_heads else N_KV // (a.shard_of or world)
         self.head_begin = 0 if full_heads else rank * self.kvl
         self.hl = self.kvl * 4
         self.dev = dev
@@ -195,11 +200,14 @@ def fqb_runner(w):
     launches = {"n": 0}
     fq.device_status_reset()
 
-    def decode(layer, qkv, bt, pos, qstart, rids, stream=None):
+    def decode(layer, qkv, bt, pos, qstart, rids, stream=None, flags=0):
         fq.attn_decode(w.q_ptr(qkv, layer), QKV_DIM, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
-                       qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream)
-        per = 512 if w.kvl == 8 else 256  # sequences one decode_kernel launch takes
-        launches["n"] += (w.batch + per - 1) // per
+                       qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
+        if flags and w.batch <= 256:
+            launches["n"] += 2 if w.kvl == 8 else 1  # 8 heads go as two launches of 4
+        else:
+            per = 512 if w.kvl == 8 else 256  # sequences one decode_kernel launch takes
+            launches["n"] += (w.batch + per - 1) // per
 
     def append(layer, qkv, bt, req, pos, stream=None):
         fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], QKV_DIM, k_off, v_off, bt, w.max_blocks, req, pos,
@@ -328,7 +336,8 @@ def main():
     cfg = {"workload": f"{w.name}, {a.layers} layers, page 16, Qwen3-8B attention shapes (32 q / 8 kv heads, d 128)",
            "layers": a.layers, "batch": a.batch, "sum_ctx": w.sum_ctx, "kv_bytes_per_layer": w.bytes_layer_total,
            "parallelism": f"kv-head shard x{world}" if not reference else "single GPU",
-           "l2": "inputs larger than L2: every layer has its own pool and the step walks all of them"}
+           "l2": "inputs larger than L2: every layer has its own pool and the step walks all of them",
+           "cuda_graph": bool(a.graph), "independent_launches": bool(a.independent)}
 
     if reference and not ref_gpu:
         # CPU arm: the oracle port on a bounded sample per step
@@ -347,15 +356,33 @@ def main():
     decode, append, launches, check = (ref_runner if reference else fqb_runner)(w)
 
     # ---- kernel-only: everything resident ----
+    dflags = 1 if (a.independent and not reference) else 0
+
     def step_resident():
         for layer in range(a.layers):
-            decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
+            if dflags:
+                decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=dflags)
+            else:
+                decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
 
+    run_step = step_resident
+    if a.graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_resident()  # warm the lazily initialised state outside the capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step_resident()
+        per_step = launches["n"] // 2
+        run_step = graph.replay
     sampler = ClockSampler(local)
     sampler.start()
     launches["n"] = 0
-    ms = time_region(step_resident, a.steps, a.warmup, dist_on, dev)
-    n_launch = launches["n"] * a.steps // (a.steps + a.warmup)
+    ms = time_region(run_step, a.steps, a.warmup, dist_on, dev)
+    n_launch = per_step * a.steps if a.graph else launches["n"] * a.steps // (a.steps + a.warmup)
     clocks = sampler.stop()
     check()
     ms_step = ms / a.steps

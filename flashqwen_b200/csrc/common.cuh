@@ -90,6 +90,15 @@ __device__ __forceinline__ void tma_load_page(void* dst, const CUtensorMap* m, u
       : "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// launch_dependents lets the next kernel on the stream (if it was launched with the programmatic
+// serialization attribute) begin while this one still runs; wait blocks until the kernel launched
+// before this one has completed and its writes are visible. Both are no-ops for plain launches.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- cp.async (16-byte, for the small q rows) -----------------------------------------------
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src)

@@ -47,6 +47,7 @@ struct DecodeParams {
   long long partial_slots;
   unsigned epoch;  // differs from launch to launch, never 0
   int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
+  int independent; // 1: nothing this launch reads is written by the kernel launched before it
 };
 
 // Scratch layout. Partial (sequence di, CTA b, kv head, q head g) lives at slot
@@ -170,6 +171,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   const int n_decode = P.n_decode;
   const int kvh = P.kvh_base + warp % HEADS, sub = warp / HEADS;
 
+  // The next kernel on the stream may start its own prologue now. This kernel's prologue reads
+  // only the step metadata (rids, qstart, pos, bt), which the kernel before it never writes.
+  pdl_launch_dependents();
   if (tid == 0) {
     tma_prefetch_desc(&tmap);
     for (int i = 0; i < NW * NS; ++i) mbar_init(&bars[i], 1);
@@ -184,18 +188,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       report(FQB_ERR_INDEX, kKidDecode, qp);
       qp = P.max_blocks * kTok - 1;
     }
-    if (qp < 0) {
-      qp = -1;
-      if (blockIdx.x == 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
-        uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(flat) * P.n_heads * kHd);
-        for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
-      }
-    }
+    if (qp < 0) qp = -1;
     s_r[di] = r;
     s_flat[di] = flat;
     s_qpos[di] = qp;
   }
+  // q, the cache and the scratch may be written by the kernel before this one: wait for it here,
+  // unless the caller declared the launch independent (then the wait moves to the very end, where
+  // it only keeps kernels completing in order).
+  if (!P.independent) pdl_wait();
   __syncthreads();
+  if (blockIdx.x == 0 && P.kvh_base == 0)
+    for (int di = tid; di < n_decode; di += NW * 32)
+      if (s_qpos[di] < 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
+        uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(s_flat[di]) * P.n_heads * kHd);
+        for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+      }
   if (warp == 0) {
     constexpr int kPer = MAXD / 32;
     int sum = 0;
@@ -225,7 +233,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   const int nb = static_cast<int>(gridDim.x);
   const int W = max(2 * SUB, (total_pages + nb - 1) / nb);  // pages per CTA
   const long long lo_ll = static_cast<long long>(blockIdx.x) * W;
-  if (lo_ll >= total_pages) return;  // whole CTA leaves together; nothing in flight
+  if (lo_ll >= total_pages) {  // whole CTA leaves together; nothing in flight
+    pdl_wait();
+    return;
+  }
   const int lo = static_cast<int>(lo_ll);
   const int hi = min(total_pages, lo + W);
   unsigned long long* counters =
@@ -472,6 +483,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       qa[ks][1] = qn[ks][1];
     }
   }
+  pdl_wait();  // a kernel never completes before the one launched ahead of it
 }
 
 }  // namespace fqb

@@ -139,9 +139,33 @@ unsigned next_epoch() {
   return e;
 }
 
+bool pdl_enabled() {
+  static const bool on = std::getenv("FQB_NO_PDL") == nullptr;  // FQB_NO_PDL=1: plain launches (debugging aid)
+  return on;
+}
+
+// Launches `kern` with or without the programmatic-serialization attribute.
+template <class... KArgs, class... Args>
+cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+// ctas_per_sm: how many CTAs of THIS launch go on each SM (the kernel may allow more to be resident,
+// so that the CTAs of the launch after it can move in beside them).
 template <class Cfg>
 int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n_decode, int sm_count,
-                  cudaStream_t st) {
+                  int ctas_per_sm, bool pdl, cudaStream_t st) {
   using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD>;
   auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD>;
   static thread_local int attr_dev = -1;
@@ -151,7 +175,7 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
     FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     attr_dev = dev;
   }
-  const int grid = sm_count * Cfg::MINB;
+  const int grid = sm_count * ctas_per_sm;
   for (int base = 0; base < n_decode; base += Cfg::MAXD) {
     P.rids = rids + base;
     P.n_decode = n_decode - base < Cfg::MAXD ? n_decode - base : Cfg::MAXD;
@@ -160,10 +184,30 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
       return set_error(FQB_ERR_WORKSPACE, "decode scratch: %lld partial slots needed, %lld given", need,
                        P.partial_slots);
     P.epoch = next_epoch();
-    kern<<<grid, Cfg::NW * 32, L::kAlloc, st>>>(map, P);
+    // a second batch of the same call shares the scratch with the first: it must not overlap it
+    FQB_CUDA_TRY(launch_ex(kern, dim3(grid), dim3(Cfg::NW * 32), L::kAlloc, st, pdl && base == 0, map, P));
   }
-  FQB_CUDA_TRY(cudaGetLastError());
   return FQB_OK;
+}
+
+// Independent launches may overlap the launch before them, so consecutive launches must not share
+// scratch. The caller's scratch is cut into regions used in rotation; the launch that wraps around
+// to region 0 is a plain launch (it waits for everything before it), so a region is never reused
+// while an earlier launch could still touch it.
+struct ScratchTurn {
+  const void* key;
+  unsigned count;
+};
+int next_region(const void* key, int regions) {
+  constexpr int kTable = 16;
+  static thread_local ScratchTurn table[kTable];
+  static thread_local int victim = 0;
+  for (int i = 0; i < kTable; ++i)
+    if (table[i].key == key) return static_cast<int>(table[i].count++ % static_cast<unsigned>(regions));
+  table[victim].key = key;
+  table[victim].count = 1;
+  victim = (victim + 1) % kTable;
+  return 0;
 }
 
 }  // namespace
@@ -186,8 +230,7 @@ int fqb_kv_append(void* cache, int num_blocks, int kv_heads_local, const void* q
     return set_error(FQB_ERR_INVALID, "kv_append: pointers, src_stride, k_off and v_off must keep 16-byte alignment");
   AppendParams P{static_cast<__nv_bfloat16*>(cache), num_blocks, kv_heads_local * kHd,
                  static_cast<const __nv_bfloat16*>(qkv), src_stride, k_off, v_off, bt, bt_stride, bt_row, pos, M};
-  kv_append_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
-  FQB_CUDA_TRY(cudaGetLastError());
+  FQB_CUDA_TRY(launch_ex(kv_append_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), true, P));
   return FQB_OK;
 }
 
@@ -215,8 +258,7 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
   P.cos_tab = cos_tab;
   P.sin_tab = sin_tab;
   P.eps = eps;
-  norm_rope_append_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
-  FQB_CUDA_TRY(cudaGetLastError());
+  FQB_CUDA_TRY(launch_ex(norm_rope_append_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), true, P));
   return FQB_OK;
 }
 
@@ -224,14 +266,15 @@ int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max
   (void)max_blocks;  // the split count follows the SM count, not the context length
   if (max_decode <= 0 || n_heads_local <= 0) return 0;
   // partials of (sequences + CTAs) segments plus the arrival counters, for one launch of at most
-  // 512 sequences on at most 512 CTAs
-  return decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512);
+  // 512 sequences on at most 512 CTAs; eight such regions so that independent launches can rotate
+  return 8 * ((decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL);
 }
 
-int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
-                    int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
-                    int n_decode, const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
-                    float* pl, float* pa, int64_t partial_slots, void* stream) {
+int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                       int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                       const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
+                       float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
+                       void* stream) {
   if (n_decode <= 0) return FQB_OK;
   if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
   if (!q || !cache || !out || !pos || !qstart || !decode_rids || !bt || !pm || !pl || !pa)
@@ -263,20 +306,59 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
   P.pl = pl;
   P.pa = pa;
   P.partial_slots = partial_slots;
+  P.independent = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  // ---- independent launches: one CTA per SM per launch, two launches resident side by side ----
+  if ((flags & FQB_DECODE_INDEPENDENT) && pdl_enabled() && n_decode <= 256) {
+    const int64_t need = (decode_slots_needed(n_decode, n_kv, di.sm_count) + 3) & ~int64_t(3);
+    int regions = static_cast<int>(partial_slots / need);
+    if (regions > 8) regions = 8;
+    if (regions >= 2) {
+      const int region = next_region(pm, regions);
+      P.pm = pm + region * need;
+      P.pl = pl + region * need;
+      P.pa = pa + region * need * kHd;
+      P.partial_slots = need;
+      P.independent = 1;
+      bool pdl = region != 0;  // the wrap-around launch drains the stream
+      for (int base = 0; base < n_kv;) {
+        const int left = n_kv - base;
+        P.kvh_base = base;
+        int rc, took;
+        if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
+        else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
+        else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        if (rc != FQB_OK) return rc;
+        base += took;
+        pdl = true;  // launches of one call serve different heads: disjoint partials and counters
+      }
+      return FQB_OK;
+    }
+  }
+
+  // ---- default: the launch waits for the kernel before it after its metadata prologue ----
   // cover the local heads with launches of 8, 4, 2 or 1 heads (one launch for 8, 4, 2, 1 heads)
   for (int base = 0; base < n_kv;) {
     const int left = n_kv - base;
     P.kvh_base = base;
     int rc, took;
-    if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, st); took = 8; }
-    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, st); took = 4; }
-    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, st); took = 2; }
-    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, st); took = 1; }
+    if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
+    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 4; }
+    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 2; }
+    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 1; }
     if (rc != FQB_OK) return rc;
     base += took;
   }
   return FQB_OK;
+}
+
+int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                    int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
+                    int n_decode, const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                    float* pl, float* pa, int64_t partial_slots, void* stream) {
+  return fqb_attn_decode_ex(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
+                            n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, 0u, stream);
 }
 
 int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,

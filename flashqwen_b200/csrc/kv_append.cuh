@@ -44,6 +44,8 @@ __device__ __forceinline__ bool append_dst(const AppendParams& P, int m, int kid
 __global__ void __launch_bounds__(256)
 kv_append_kernel(const AppendParams P) {
   const int m = blockIdx.x;
+  pdl_launch_dependents();  // the attention kernel that follows may run its metadata prologue now
+  pdl_wait();               // the rows were produced by the kernel before this one
   long long dst;
   if (!append_dst(P, m, kKidAppend, dst)) return;
   const int vecs = P.row_elems / 8;  // 16-byte vectors per plane row
@@ -76,6 +78,8 @@ __global__ void __launch_bounds__(256)
 norm_rope_append_kernel(const NormRopeParams P) {
   const int m = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
   long long dst;
   const bool ok = append_dst(P.a, m, kKidNormRope, dst);
   __nv_bfloat16* row = const_cast<__nv_bfloat16*>(P.a.qkv) + static_cast<long long>(m) * P.a.src_stride;

@@ -56,12 +56,16 @@ def decode_partial_slots(max_decode, n_heads_local, max_blocks):
     return lib.fqb_attn_decode_partial_slots(max_decode, n_heads_local, max_blocks)
 
 
+DECODE_INDEPENDENT = 1
+
+
 def attn_decode(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
-                bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, stream=None):
-    """fqb_attn_decode; reference: LaunchAttnDecodeCute, engine/src/attn_cute.h:14-20."""
-    check(lib.fqb_attn_decode(_ptr(q), q_stride, _ptr(cache_kv), num_blocks, _ptr(out), n_heads, n_kv, head_dim,
-                              _ptr(pos), _ptr(qstart), _ptr(decode_rids), n_decode, _ptr(bt), max_blocks, block_size,
-                              scale, _ptr(pm), _ptr(pl), _ptr(pa), partial_slots, _stream(stream)), "fqb_attn_decode")
+                bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, stream=None, flags=0):
+    """fqb_attn_decode(_ex); reference: LaunchAttnDecodeCute, engine/src/attn_cute.h:14-20."""
+    check(lib.fqb_attn_decode_ex(_ptr(q), q_stride, _ptr(cache_kv), num_blocks, _ptr(out), n_heads, n_kv, head_dim,
+                                 _ptr(pos), _ptr(qstart), _ptr(decode_rids), n_decode, _ptr(bt), max_blocks,
+                                 block_size, scale, _ptr(pm), _ptr(pl), _ptr(pa), partial_slots, flags,
+                                 _stream(stream)), "fqb_attn_decode")
 
 
 def attn_prefill(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, qlen, rids, R, max_qlen,

@@ -109,6 +109,24 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
                     int block_size, float scale, float* pm, float* pl, float* pa,
                     int64_t partial_slots, void* stream);
 
+/* fqb_attn_decode with flags. Every launch of this library lets the kernel after it begin early
+ * (programmatic dependent launch) and itself waits for the kernel before it only after its own
+ * prologue, which reads nothing but pos / qstart / decode_rids / bt -- those four arrays must not be
+ * written by the kernel launched immediately before this call (the engine fills them with copies at
+ * the start of the step, engine/src/model_runtime.cu:295-302).
+ *   FQB_DECODE_INDEPENDENT  the caller states that the kernel launched immediately before this call
+ *       writes NOTHING this call reads (q, cache, metadata) and does not read `out`. The launch then
+ *       streams KV while that kernel is still running; consecutive calls rotate through up to 8
+ *       regions of the scratch and every wrap-around launch waits for all earlier work, so scratch is
+ *       never shared by two live launches. Meant for back-to-back attention over independent
+ *       caches (micro-batches, benchmarks); without the flag the call is always safe. */
+#define FQB_DECODE_INDEPENDENT 1u
+int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
+                       int n_heads, int n_kv, int head_dim, const int32_t* pos,
+                       const int32_t* qstart, const int32_t* decode_rids, int n_decode,
+                       const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                       float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
+
 /* ---- kernel 3: chunked-prefill paged attention ---------------------------------------------
  * replaces: engine/src/attn_cute.h:7-12 LaunchAttnPrefillCute (engine/src/attn_cute.cu:30-163).
  * For prefill request r = rids[z], z < R: rows qstart[r] .. qstart[r]+qlen[r]-1 are contiguous,

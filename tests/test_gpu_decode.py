@@ -156,3 +156,59 @@ def test_linearity_in_v_at_config2_size():
     pick = np.asarray([int(np.argmin(lengths)), int(np.argmax(lengths)), 17], np.int32)
     want = O.attn_decode(c.qkv, 6144, hc, 32, 8, c.pos, c.qstart, pick, c.bt, c.scale, rows=64)
     assert maxabs(base[pick], want[pick]) <= TOL
+
+
+@pytest.mark.parametrize("flags", [0, 1])
+@pytest.mark.parametrize("n_kv", [8, 2])
+def test_back_to_back_launches_share_scratch_safely(flags, n_kv):
+    """Many launches in a row on one stream with one scratch and no host sync in between, as a layer
+    loop issues them: default launches wait for their predecessor after the prologue, independent
+    launches (flags=1) overlap it and rotate through regions of the scratch."""
+    layers = 13
+    cs = [synth.decode_case([700, 33, 1500, 16, 250, 4000], 520, seed=200 + i, n_kv=n_kv) for i in range(3)]
+    caches = [dv(c.cache) for c in cs]
+    qkvs = [dv(c.qkv) for c in cs]
+    metas = [(dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt)) for c in cs]
+    outs = [torch.full((6, n_kv * 4 * 128), 0x7FC0, dtype=torch.int16, device=DEV) for _ in range(layers)]
+    s = Scratch(6, n_kv * 4, cs[0].max_blocks)
+    for rep in range(2):
+        for layer in range(layers):
+            c, k = cs[layer % 3], layer % 3
+            pos, qstart, rids, bt = metas[k]
+            fq.attn_decode(qkvs[k], c.q_stride, caches[k], c.num_blocks, outs[layer], n_kv * 4, n_kv, 128, pos,
+                           qstart, rids, 6, bt, c.max_blocks, 16, c.scale, s.pm, s.pl, s.pa, s.slots, flags=flags)
+    torch.cuda.synchronize()
+    fq.device_status()
+    want = [oracle_decode(c) for c in cs]
+    for layer in range(layers):
+        assert maxabs(host(outs[layer]), want[layer % 3]) <= TOL, layer
+
+
+def test_decode_inside_a_cuda_graph_with_changing_lengths():
+    """The launch geometry does not depend on context lengths: a captured step replays correctly
+    after the lengths (pos) and block tables change under it."""
+    c1 = synth.decode_case([100, 900, 17, 3000], 300, seed=300, n_kv=8, max_blocks=256)
+    c2 = synth.decode_case([2500, 5, 640, 31], 300, seed=301, n_kv=8, max_blocks=256)
+    cache, qkv = dv(c1.cache), dv(c1.qkv)
+    pos, qstart, rids, bt = dv(c1.pos), dv(c1.qstart), dv(c1.decode_rids), dv(c1.bt)
+    out = torch.zeros((4, 32 * 128), dtype=torch.int16, device=DEV)
+    s = Scratch(4, 32, 256)
+
+    def step():
+        fq.attn_decode(qkv, c1.q_stride, cache, 300, out, 32, 8, 128, pos, qstart, rids, 4, bt, 256, 16, c1.scale,
+                       s.pm, s.pl, s.pa, s.slots)
+
+    step()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    g.replay()
+    torch.cuda.synchronize()
+    assert maxabs(host(out), oracle_decode(c1)) <= TOL
+    cache.copy_(dv(c2.cache)); qkv.copy_(dv(c2.qkv)); pos.copy_(dv(c2.pos)); bt.copy_(dv(c2.bt))
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    fq.device_status()
+    assert maxabs(host(out), oracle_decode(c2)) <= TOL
