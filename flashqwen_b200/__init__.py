@@ -12,6 +12,7 @@ from .ops import (  # noqa: F401
     DECODE_INDEPENDENT,
     KvStore,
     attn_decode,
+    attn_decode_static,
     attn_prefill,
     copy_blocks,
     copy_blocks_layers,

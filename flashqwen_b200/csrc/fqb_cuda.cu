@@ -361,6 +361,56 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
                             n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, 0u, stream);
 }
 
+// ---- decode attention for callers that cannot provide scratch -------------------------------------
+// Scratch of fqb_attn_decode_static: pm | pl | pa for kStaticSlots partial slots, 4.06 MiB, part of
+// the library image on every GPU that loads it. Device code could name the array directly; host
+// code cannot -- on the host the symbol is only a stand-in -- so its device address is looked up
+// once per device with cudaGetSymbolAddress and handed to the kernel like any caller's scratch.
+constexpr long long kStaticSlots = 8192;
+static __device__ __align__(256) float g_decode_static_scratch[kStaticSlots * (2 + FQB_HEAD_DIM)];
+
+namespace fqb {
+namespace {
+int static_scratch_address(float** out) {
+  static std::mutex mu;
+  static float* addr[64] = {};
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(FQB_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (!addr[dev]) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_static_scratch);
+    if (e != cudaSuccess || !p)
+      return set_error(FQB_ERR_CUDA, "attn_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                       cudaGetErrorString(e));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return FQB_OK;
+}
+}  // namespace
+}  // namespace fqb
+
+int fqb_attn_decode_static(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                           int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                           const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks,
+                           int block_size, float scale, void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (n_decode > FQB_STATIC_MAX_DECODE || n_kv > FQB_STATIC_MAX_KV_HEADS)
+    return set_error(FQB_ERR_WORKSPACE,
+                     "attn_decode_static: %d sequences x %d kv heads is beyond the built-in scratch "
+                     "(at most %d sequences, %d kv heads); use fqb_attn_decode with your own scratch",
+                     n_decode, n_kv, FQB_STATIC_MAX_DECODE, FQB_STATIC_MAX_KV_HEADS);
+  float* base = nullptr;
+  if (int rc = fqb::static_scratch_address(&base)) return rc;
+  // the arrival counters inside the scratch are tagged with a per-launch number, so nothing has to
+  // be zeroed between calls even though the array keeps the previous call's contents
+  return fqb_attn_decode_ex(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
+                            n_decode, bt, max_blocks, block_size, scale, base, base + kStaticSlots,
+                            base + 2 * kStaticSlots, kStaticSlots, 0u, stream);
+}
+
 int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
                      int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart, const int32_t* qlen,
                      const int32_t* rids, int R, int max_qlen, const int32_t* bt, int max_blocks, int block_size,

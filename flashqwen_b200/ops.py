@@ -68,6 +68,15 @@ def attn_decode(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim,
                                  _stream(stream)), "fqb_attn_decode")
 
 
+def attn_decode_static(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
+                       n_decode, bt, max_blocks, block_size, scale, stream=None):
+    """fqb_attn_decode_static: decode attention with the library's built-in scratch, for callers that
+    cannot allocate any (at most 64 sequences and 8 kv heads per call; one call at a time per GPU)."""
+    check(lib.fqb_attn_decode_static(_ptr(q), q_stride, _ptr(cache_kv), num_blocks, _ptr(out), n_heads, n_kv,
+                                     head_dim, _ptr(pos), _ptr(qstart), _ptr(decode_rids), n_decode, _ptr(bt),
+                                     max_blocks, block_size, scale, _stream(stream)), "fqb_attn_decode_static")
+
+
 def attn_prefill(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, qlen, rids, R, max_qlen,
                  bt, max_blocks, block_size, scale, stream=None):
     """fqb_attn_prefill; reference: LaunchAttnPrefillCute, engine/src/attn_cute.h:7-12."""

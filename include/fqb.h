@@ -127,6 +127,33 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
                        const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
                        float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
 
+/* Decode attention without caller scratch. No counterpart in the reference (its call site always
+ * passes pm / pl / pa): this entry point exists for callers that have no device memory to give and
+ * no way to get any at the point of the call -- an engine that handed all free VRAM to its KV pool
+ * at start-up, as the FlashQwen engine does (engine/src/kv_store.cu:10-46), so a later cudaMalloc
+ * fails; code between cudaStreamBeginCapture and cudaStreamEndCapture, where cudaMalloc is not
+ * allowed; a plugin inside a host that owns every device allocation. It runs the same kernel as
+ * fqb_attn_decode with the split-K scratch taken from a fixed 4.06 MiB array inside the library's
+ * own device image (resident on every GPU that loads the library until the process exits), and it
+ * calls no allocating routine of any kind.
+ *   Limits: n_decode <= FQB_STATIC_MAX_DECODE and n_kv <= FQB_STATIC_MAX_KV_HEADS; beyond them the
+ *   call returns FQB_ERR_WORKSPACE and launches nothing (so does the full 64 x 8 case on a GPU with
+ *   more than 159 SMs, where it no longer fits the array; B200 has 148).
+ *   First call on each device: looks up the array's device address (cudaGetSymbolAddress, with that
+ *   device current). Make that first call outside any stream capture; later calls may be captured
+ *   like the other operators.
+ *   All calls on a device share the one array, which keeps whatever the previous call left in it.
+ *   Nothing in it needs clearing (the arrival counters are tagged per launch), but two calls whose
+ *   kernels can overlap on the GPU -- different streams, or FQB_DECODE_INDEPENDENT-style pipelining --
+ *   race on it: issue them on one stream, one after the other. */
+#define FQB_STATIC_MAX_DECODE 64
+#define FQB_STATIC_MAX_KV_HEADS 8
+int fqb_attn_decode_static(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
+                           int n_heads, int n_kv, int head_dim, const int32_t* pos,
+                           const int32_t* qstart, const int32_t* decode_rids, int n_decode,
+                           const int32_t* bt, int max_blocks, int block_size, float scale,
+                           void* stream);
+
 /* ---- kernel 3: chunked-prefill paged attention ---------------------------------------------
  * replaces: engine/src/attn_cute.h:7-12 LaunchAttnPrefillCute (engine/src/attn_cute.cu:30-163).
  * For prefill request r = rids[z], z < R: rows qstart[r] .. qstart[r]+qlen[r]-1 are contiguous,
