@@ -58,9 +58,10 @@ def parse():
     ap.add_argument("--ref-kind", default="auto", choices=["auto", "gpu", "cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--graph", action="store_true", help="replay the resident step from a CUDA graph")
-    ap.add_argument("--independent", action="store_true",
-                    help="resident loop: pass FQB_DECODE_INDEPENDENT (the layers of the synthetic step are independent)")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="issue the resident step launch by launch instead of replaying a CUDA graph")
+    ap.add_argument("--dependent", dest="independent", action="store_false",
+                    help="resident loop without FQB_DECODE_INDEPENDENT: every launch waits for the one before it")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="tuning aid: run rank 0's share of an N-way kv-head shard on this one GPU")
     return ap.parse_args()
@@ -170,12 +171,19 @@ class Workload:
                 k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + 1e-6)
                 t[b0:b0 + step, 0] = k.view(-1, PAGE, self.kvl * HD).to(torch.bfloat16)
             self.pools.append(t)
-        # fused qkv rows of the step, all layers: [layers][batch][6144]; q per-head unit RMS
+        # fused qkv rows of the step, all layers; q and k per-head unit RMS. A rank holds its own
+        # columns [q heads local | k heads local | v heads local], as a head-parallel QKV projection
+        # would produce them (the full 6144-wide row on one GPU).
         gh = torch.Generator().manual_seed(a.seed + 7)
         qkv = torch.randn((a.layers, a.batch, QKV_DIM), generator=gh, dtype=torch.float32)
         q = qkv[:, :, :Q_DIM + KV_DIM].view(a.layers, a.batch, N_HEADS + N_KV, HD)
         q.mul_(torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6))
-        self.h_qkv = qkv.to(torch.bfloat16).pin_memory()
+        hb, kb = self.head_begin * 4 * HD, self.head_begin * HD
+        local = torch.cat([qkv[:, :, hb:hb + self.hl * HD], qkv[:, :, Q_DIM + kb:Q_DIM + kb + self.kvl * HD],
+                           qkv[:, :, Q_DIM + KV_DIM + kb:Q_DIM + KV_DIM + kb + self.kvl * HD]], dim=-1)
+        self.row_dim = (self.hl + 2 * self.kvl) * HD
+        self.k_off, self.v_off = self.hl * HD, (self.hl + self.kvl) * HD
+        self.h_qkv = local.to(torch.bfloat16).contiguous().pin_memory()
         self.qkv = self.h_qkv.to(dev)
         self.out = torch.zeros((a.layers, a.batch, self.hl * HD), dtype=torch.bfloat16, device=dev)
         self.h_out = torch.zeros((a.layers, a.batch, self.hl * HD), dtype=torch.bfloat16).pin_memory()
@@ -185,8 +193,6 @@ class Workload:
         self.bytes_layer_total = self.sum_ctx * 2 * KV_DIM * 2 + a.batch * 2 * Q_DIM * 2
         self.scale = HD ** -0.5
 
-    def q_ptr(self, qkv, layer):
-        return qkv[layer].data_ptr() + self.head_begin * 4 * HD * 2
 
 
 def fqb_runner(w):
@@ -196,12 +202,11 @@ def fqb_runner(w):
     pm = torch.empty(slots, device=w.dev)
     pl = torch.empty(slots, device=w.dev)
     pa = torch.empty(slots * HD, device=w.dev)
-    k_off, v_off = Q_DIM + w.head_begin * HD, Q_DIM + KV_DIM + w.head_begin * HD
     launches = {"n": 0}
     fq.device_status_reset()
 
     def decode(layer, qkv, bt, pos, qstart, rids, stream=None, flags=0):
-        fq.attn_decode(w.q_ptr(qkv, layer), QKV_DIM, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
+        fq.attn_decode(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
                        qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
         if flags and w.batch <= 256:
             launches["n"] += 2 if w.kvl == 8 else 1  # 8 heads go as two launches of 4
@@ -210,8 +215,8 @@ def fqb_runner(w):
             launches["n"] += (w.batch + per - 1) // per
 
     def append(layer, qkv, bt, req, pos, stream=None):
-        fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], QKV_DIM, k_off, v_off, bt, w.max_blocks, req, pos,
-                     w.batch, stream)
+        fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, w.k_off, w.v_off, bt, w.max_blocks,
+                     req, pos, w.batch, stream)
         launches["n"] += 1
 
     def check():
@@ -356,39 +361,49 @@ def main():
     decode, append, launches, check = (ref_runner if reference else fqb_runner)(w)
 
     # ---- kernel-only: everything resident ----
+    def measure_resident(flags, use_graph):
+        def step_resident():
+            for layer in range(a.layers):
+                if flags:
+                    decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=flags)
+                else:
+                    decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
+
+        run_step, per_step = step_resident, None
+        if use_graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_resident()  # warm the lazily initialised state outside the capture
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            launches["n"] = 0
+            with torch.cuda.graph(graph):
+                step_resident()
+            per_step = launches["n"]
+            run_step = graph.replay
+        launches["n"] = 0
+        t = time_region(run_step, a.steps, a.warmup, dist_on, dev)
+        n = per_step * a.steps if use_graph else launches["n"] * a.steps // (a.steps + a.warmup)
+        return t, n
+
     dflags = 1 if (a.independent and not reference) else 0
-
-    def step_resident():
-        for layer in range(a.layers):
-            if dflags:
-                decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=dflags)
-            else:
-                decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
-
-    run_step = step_resident
-    if a.graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step_resident()  # warm the lazily initialised state outside the capture
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step_resident()
-        per_step = launches["n"] // 2
-        run_step = graph.replay
     sampler = ClockSampler(local)
     sampler.start()
-    launches["n"] = 0
-    ms = time_region(run_step, a.steps, a.warmup, dist_on, dev)
-    n_launch = per_step * a.steps if a.graph else launches["n"] * a.steps // (a.steps + a.warmup)
+    ms, n_launch = measure_resident(dflags, a.graph)
     clocks = sampler.stop()
     check()
     ms_step = ms / a.steps
     value = w.bytes_layer_total * a.layers / (ms_step * 1e-3) / 1e9
     layer_s = ms_step * 1e-3 / a.layers
     achieved = w.bytes_layer_rank / layer_s / 1e9
+    dependent = None
+    if dflags:  # the same step with every launch waiting for the one before it
+        ms_d, _ = measure_resident(0, a.graph)
+        check()
+        dependent = {"ms_per_step": round(ms_d / a.steps, 4),
+                     "value": round(w.bytes_layer_total * a.layers / (ms_d / a.steps * 1e-3) / 1e9, 2), "unit": "GB/s"}
 
     # ---- attention + all-gather of the per-head outputs (N > 1) ----
     gather_ms = None
@@ -412,26 +427,44 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in (w.h_qkv, w.h_bt, w.h_pos, w.h_qstart, w.h_rids, w.h_req))
         d2h = w.h_out.numel() * w.h_out.element_size()
 
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        group = 6  # layers per copy chunk: copies of chunk i+1 overlap the kernels of chunk i
+        chunks = [(l0, min(a.layers, l0 + group)) for l0 in range(0, a.layers, group)]
+        ev_in = [torch.cuda.Event() for _ in chunks]
+        ev_out = [torch.cuda.Event() for _ in chunks]
+
         def step_e2e():
-            d_bt.copy_(w.h_bt, non_blocking=True)
-            d_pos.copy_(w.h_pos, non_blocking=True)
-            d_qstart.copy_(w.h_qstart, non_blocking=True)
-            d_rids.copy_(w.h_rids, non_blocking=True)
-            d_req.copy_(w.h_req, non_blocking=True)
-            d_qkv.copy_(w.h_qkv, non_blocking=True)
-            for layer in range(a.layers):
-                append(layer, d_qkv, d_bt, d_req, d_pos)
-                decode(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids)
-                if dist_on:
-                    torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
-            w.h_out.copy_(w.out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+            main = torch.cuda.current_stream()
+            copy_in.wait_stream(main)
+            copy_out.wait_stream(main)
+            with torch.cuda.stream(copy_in):
+                d_bt.copy_(w.h_bt, non_blocking=True)
+                d_pos.copy_(w.h_pos, non_blocking=True)
+                d_qstart.copy_(w.h_qstart, non_blocking=True)
+                d_rids.copy_(w.h_rids, non_blocking=True)
+                d_req.copy_(w.h_req, non_blocking=True)
+                for i, (l0, l1) in enumerate(chunks):
+                    d_qkv[l0:l1].copy_(w.h_qkv[l0:l1], non_blocking=True)
+                    ev_in[i].record(copy_in)
+            for i, (l0, l1) in enumerate(chunks):
+                main.wait_event(ev_in[i])
+                for layer in range(l0, l1):
+                    append(layer, d_qkv, d_bt, d_req, d_pos)
+                    decode(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids)
+                    if dist_on:
+                        torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
+                ev_out[i].record(main)
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(ev_out[i])
+                    w.h_out[l0:l1].copy_(w.out[l0:l1], non_blocking=True)
+            main.wait_stream(copy_out)
+            main.synchronize()  # the caller reads the result every step
 
         ms_e = time_region(step_e2e, a.steps, a.warmup, dist_on, dev) / a.steps
         check()
         e2e = {"value": round(w.bytes_layer_total * a.layers / (ms_e * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(ms_e, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "includes": "H2D of qkv rows + metadata, per-layer KV append + decode attention"
+               "includes": "H2D of qkv rows + metadata (chunks of 6 layers on a copy stream), per-layer KV append + decode attention"
                            + (", NCCL all-gather of head outputs" if dist_on else "") + ", D2H of the output"}
 
     if rank != 0:
@@ -449,6 +482,8 @@ def main():
                          "algorithmic_bytes_per_launch": w.bytes_layer_rank,
                          "launch_us": round(layer_s * 1e6, 3)},
             "clocks": clocks, "gpu_launches": n_launch}
+    if dependent is not None:
+        line["dependent_launches"] = dependent
     if gather_ms is not None:
         line["with_all_gather"] = {"ms_per_step": round(gather_ms, 4),
                                    "value": round(w.bytes_layer_total * a.layers / (gather_ms * 1e-3) / 1e9, 2)}
@@ -459,7 +494,7 @@ def main():
         line["cpu_baseline"] = {"value": round(value, 2), "unit": "GB/s", "cores": 0, "kind": "reference",
                                 "sample": "the reference has no CPU implementation of this path: its own CUDA kernels "
                                           "(kv_store.cu, attn_cute.cu rebuilt for sm_100a) on the full workload, 1 GPU"}
-    elif not a.no_cpu_baseline and a.gpus == 1:
+    elif not a.no_cpu_baseline and a.gpus == 1 and w.row_dim == QKV_DIM:
         line["cpu_baseline"] = cpu_oracle_rate(w, a)
     print(json.dumps(line))
     if dist_on:

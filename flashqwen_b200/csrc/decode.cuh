@@ -48,6 +48,7 @@ struct DecodeParams {
   unsigned epoch;  // differs from launch to launch, never 0
   int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
   int independent; // 1: nothing this launch reads is written by the kernel launched before it
+  int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
 };
 
 // Scratch layout. Partial (sequence di, CTA b, kv head, q head g) lives at slot
@@ -173,7 +174,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
 
   // The next kernel on the stream may start its own prologue now. This kernel's prologue reads
   // only the step metadata (rids, qstart, pos, bt), which the kernel before it never writes.
-  pdl_launch_dependents();
+  if (!P.sync_first) pdl_launch_dependents();
   if (tid == 0) {
     tma_prefetch_desc(&tmap);
     for (int i = 0; i < NW * NS; ++i) mbar_init(&bars[i], 1);
@@ -196,7 +197,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   // q, the cache and the scratch may be written by the kernel before this one: wait for it here,
   // unless the caller declared the launch independent (then the wait moves to the very end, where
   // it only keeps kernels completing in order).
-  if (!P.independent) pdl_wait();
+  // A sync_first launch (the one that re-enters scratch region 0) waits first and only then lets
+  // the next launch start, so every launch after it begins with all older launches complete.
+  if (!P.independent || P.sync_first) pdl_wait();
+  if (P.sync_first) pdl_launch_dependents();
   __syncthreads();
   if (blockIdx.x == 0 && P.kvh_base == 0)
     for (int di = tid; di < n_decode; di += NW * 32)

@@ -131,6 +131,9 @@ using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
+// independent launches with 2 or 1 local heads: three small CTAs (of three different launches) per SM
+using DecodeCfg2i = DecodeCfg<2, 4, 2, 3, 256>;
+using DecodeCfg1i = DecodeCfg<2, 4, 1, 3, 256>;
 
 unsigned next_epoch() {
   static std::atomic<unsigned> counter{0x5eed0000u};
@@ -194,6 +197,7 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
 // scratch. The caller's scratch is cut into regions used in rotation; the launch that wraps around
 // to region 0 is a plain launch (it waits for everything before it), so a region is never reused
 // while an earlier launch could still touch it.
+constexpr int kMaxRegions = 16;
 struct ScratchTurn {
   const void* key;
   unsigned count;
@@ -266,8 +270,8 @@ int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max
   (void)max_blocks;  // the split count follows the SM count, not the context length
   if (max_decode <= 0 || n_heads_local <= 0) return 0;
   // partials of (sequences + CTAs) segments plus the arrival counters, for one launch of at most
-  // 512 sequences on at most 512 CTAs; eight such regions so that independent launches can rotate
-  return 8 * ((decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL);
+  // 512 sequences on at most 512 CTAs; sixteen such regions so that independent launches can rotate
+  return 16 * ((decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL);
 }
 
 int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -307,13 +311,16 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
   P.pa = pa;
   P.partial_slots = partial_slots;
   P.independent = 0;
+  P.sync_first = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // ---- independent launches: one CTA per SM per launch, two launches resident side by side ----
   if ((flags & FQB_DECODE_INDEPENDENT) && pdl_enabled() && n_decode <= 256) {
     const int64_t need = (decode_slots_needed(n_decode, n_kv, di.sm_count) + 3) & ~int64_t(3);
     int regions = static_cast<int>(partial_slots / need);
-    if (regions > 8) regions = 8;
+    if (regions > kMaxRegions) regions = kMaxRegions;
+    static const int region_cap = std::getenv("FQB_DECODE_REGIONS") ? std::atoi(std::getenv("FQB_DECODE_REGIONS")) : 0;
+    if (region_cap >= 2 && regions > region_cap) regions = region_cap;  // tuning aid
     if (regions >= 2) {
       const int region = next_region(pm, regions);
       P.pm = pm + region * need;
@@ -321,17 +328,21 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
       P.pa = pa + region * need * kHd;
       P.partial_slots = need;
       P.independent = 1;
-      bool pdl = region != 0;  // the wrap-around launch drains the stream
+      // The launch that re-enters region 0 waits for all earlier kernels before it lets the next
+      // launch start (sync_first): a region is reused 16 launches later, and between any launch and
+      // the one 16 before it lies such a sync point, so the earlier user has always completed.
+      P.sync_first = region == 0 ? 1 : 0;
+      const bool pdl = true;
       for (int base = 0; base < n_kv;) {
         const int left = n_kv - base;
         P.kvh_base = base;
         int rc, took;
         if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
-        else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        else if (left >= 2) { rc = launch_decode<DecodeCfg2i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
+        else { rc = launch_decode<DecodeCfg1i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
-        pdl = true;  // launches of one call serve different heads: disjoint partials and counters
+        P.sync_first = 0;  // later launches of the call serve other heads: disjoint partials and counters
       }
       return FQB_OK;
     }

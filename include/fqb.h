@@ -116,9 +116,9 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
  * the start of the step, engine/src/model_runtime.cu:295-302).
  *   FQB_DECODE_INDEPENDENT  the caller states that the kernel launched immediately before this call
  *       writes NOTHING this call reads (q, cache, metadata) and does not read `out`. The launch then
- *       streams KV while that kernel is still running; consecutive calls rotate through up to 8
- *       regions of the scratch and every wrap-around launch waits for all earlier work, so scratch is
- *       never shared by two live launches. Meant for back-to-back attention over independent
+ *       streams KV while that kernel is still running; consecutive calls rotate through up to 16
+ *       regions of the scratch and the launch that re-enters the first region completes all earlier
+ *       work before any later launch may start, so scratch is never shared by two live launches. Meant for back-to-back attention over independent
  *       caches (micro-batches, benchmarks); without the flag the call is always safe. */
 #define FQB_DECODE_INDEPENDENT 1u
 int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
