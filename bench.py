@@ -62,6 +62,9 @@ def parse():
                     help="issue the resident step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--dependent", dest="independent", action="store_false",
                     help="resident loop without FQB_DECODE_INDEPENDENT: every launch waits for the one before it")
+    ap.add_argument("--workload", default="decode", choices=["decode", "cfg3", "copy"],
+                    help="decode: the headline step. cfg3: KV append + chunked prefill (4 x 512-row chunks over "
+                         "histories 0/1024/3000/7000). copy: prefix-block copy-on-write copies over 36 layers")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="tuning aid: run rank 0's share of an N-way kv-head shard on this one GPU")
     return ap.parse_args()
@@ -308,8 +311,160 @@ def cpu_oracle_rate(w, a, budget_s=20.0):
                       f"of scalar oracle time on {cores} threads"}
 
 
+def event_ms(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured (MEASURED_PEAKS.json, burst)"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def run_cfg3(a, dev):
+    """Configuration 3 on one GPU: 4 sequences with 0/1024/3000/7000 cached tokens each receive a
+    512-row chunk (token budget 2048): fused RMSNorm + RoPE + KV append, then causal paged attention
+    of the chunk over its full history. Prints one JSON line (secondary workload, not the headline)."""
+    import flashqwen_b200 as fq
+
+    hist, chunk = [0, 1024, 3000, 7000], 512
+    n_req, rows = len(hist), 4 * chunk
+    max_blocks = 8192 // PAGE
+    need = sum((h + chunk + PAGE - 1) // PAGE for h in hist)
+    num_blocks = need + 64
+    rng = np.random.default_rng(a.seed)
+    perm = rng.permutation(num_blocks).astype(np.int32)
+    bt = np.zeros((n_req, max_blocks), np.int32)
+    used = 0
+    for r, h in enumerate(hist):
+        nb = (h + chunk + PAGE - 1) // PAGE
+        bt[r, :nb] = perm[used:used + nb]
+        used += nb
+    pos = np.concatenate([np.arange(h, h + chunk) for h in hist]).astype(np.int32)
+    req = np.repeat(np.arange(n_req), chunk).astype(np.int32)
+    g = torch.Generator(device=dev).manual_seed(a.seed)
+    # several pools / row sets so that consecutive iterations do not find their data in L2
+    nset = 8
+    pools = [torch.empty((num_blocks, 2, PAGE, KV_DIM), dtype=torch.bfloat16, device=dev).normal_(generator=g)
+             for _ in range(nset)]
+    qkvs = [torch.empty((rows, QKV_DIM), dtype=torch.bfloat16, device=dev).normal_(generator=g) for _ in range(nset)]
+    outs = [torch.zeros((rows, Q_DIM), dtype=torch.bfloat16, device=dev) for _ in range(nset)]
+    from flashqwen_b200 import synth
+    cos, sin = synth.rope_tables(8192)
+    d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)  # noqa: E731
+    bt_d, pos_d, req_d, cos_d, sin_d = d(bt), d(pos), d(req), d(cos), d(sin)
+    w1 = torch.ones(HD, device=dev)
+    qstart_d = d(np.arange(0, rows, chunk).astype(np.int32))
+    qlen_d = d(np.full(n_req, chunk, np.int32))
+    rids_d = d(np.arange(n_req, dtype=np.int32))
+    scale = HD ** -0.5
+    reference = a.impl == "reference"
+    if reference:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib
+        ref = oracle_lib.ref_cuda()
+        if ref is None:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libfq_ref_cuda.so not built"}))
+            return
+    it = {"i": 0}
+
+    def st():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def append_step():
+        i = it["i"] = (it["i"] + 1) % nset
+        if reference:
+            ref.ref_head_norm_rope(qkvs[i].data_ptr(), w1.data_ptr(), w1.data_ptr(), cos_d.data_ptr(), sin_d.data_ptr(),
+                                   pos_d.data_ptr(), rows, N_HEADS, N_KV, HD, QKV_DIM, 1e-6, st())
+            ref.ref_store_kv(pools[i].data_ptr(), N_HEADS, N_KV, HD, qkvs[i].data_ptr(), bt_d.data_ptr(), max_blocks,
+                             req_d.data_ptr(), pos_d.data_ptr(), rows, st())
+        else:
+            fq.norm_rope_append(pools[i], num_blocks, N_KV, N_HEADS, qkvs[i], QKV_DIM, 0, Q_DIM, Q_DIM + KV_DIM, w1, w1,
+                                cos_d, sin_d, 1e-6, bt_d, max_blocks, req_d, pos_d, rows)
+
+    def prefill_step():
+        i = it["i"] = (it["i"] + 1) % nset
+        if reference:
+            ref.ref_attn_prefill(qkvs[i].data_ptr(), QKV_DIM, pools[i].data_ptr(), outs[i].data_ptr(), N_HEADS, N_KV, HD,
+                                 pos_d.data_ptr(), qstart_d.data_ptr(), qlen_d.data_ptr(), rids_d.data_ptr(), n_req,
+                                 chunk, bt_d.data_ptr(), max_blocks, PAGE, scale, st())
+        else:
+            fq.attn_prefill(qkvs[i], QKV_DIM, pools[i], num_blocks, outs[i], N_HEADS, N_KV, HD, pos_d, qstart_d, qlen_d,
+                            rids_d, n_req, chunk, bt_d, max_blocks, PAGE, scale)
+
+    for i in range(nset):  # rows normalised + appended once so that the attention sees sane values
+        it["i"] = i - 1
+        append_step()
+    ms_app = event_ms(append_step, a.steps, a.warmup)
+    ms_pre = event_ms(prefill_step, a.steps, a.warmup)
+    if not reference:
+        fq.device_status()
+    flops = float(sum(N_HEADS * 4 * HD * (p + 1) for p in pos.tolist()))
+    peak, src = tensor_peak()
+    tf = flops / (ms_pre * 1e-3) / 1e12
+    app_bytes = rows * (2 * (Q_DIM + KV_DIM) * 2 + KV_DIM * 2 + 2 * KV_DIM * 2)  # q,k read+written, v read, k,v stored
+    print(json.dumps({
+        "metric": "chunked_prefill_attn_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_pre, 4), "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic", "impl": a.impl,
+        "config": {"workload": "cfg3: 4 x 512-row chunks over histories 0/1024/3000/7000, token budget 2048, page 16",
+                   "flops": flops, "l2": f"{nset} rotating pools and row sets"},
+        "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(tf / peak, 4), "traffic": None, "peak_source": src},
+        "append": {"kernel": "norm_rope_append (RMSNorm + RoPE + KV append)" if not reference else
+                   "LaunchHeadNormRope + StoreKvKernel", "ms": round(ms_app, 4),
+                   "GB/s": round(app_bytes / (ms_app * 1e-3) / 1e9, 1), "bytes": app_bytes}}))
+
+
+def run_copy(a, dev):
+    """Copy-on-write copies of configuration 5's variant: 256 (shared, private) page pairs copied in
+    all 36 layers by one launch."""
+    import flashqwen_b200 as fq
+
+    layers, pairs_n, num_blocks = a.layers, 256, 4096
+    pools = [torch.empty((num_blocks, 2, PAGE, KV_DIM), dtype=torch.bfloat16, device=dev).normal_() for _ in range(layers)]
+    ptrs = torch.tensor([t.data_ptr() for t in pools], dtype=torch.int64, device=dev)
+    rng = np.random.default_rng(a.seed)
+    ids = rng.permutation(num_blocks)[:2 * pairs_n].astype(np.int32)
+    pairs = torch.from_numpy(np.stack([ids[:pairs_n], ids[pairs_n:]], 1).reshape(-1).copy()).to(dev)
+    fn = lambda: fq.copy_blocks_layers(ptrs, layers, num_blocks, N_KV, pairs, pairs_n)  # noqa: E731
+    ms = event_ms(fn, a.steps, a.warmup)
+    fq.device_status()
+    nbytes = 2 * pairs_n * 65536 * layers
+    peak, src = hbm_peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "prefix_block_copy_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
+                      "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+                      "dtype": "u8", "data": "synthetic",
+                      "config": {"workload": f"{pairs_n} page pairs x {layers} layers, 64 KiB pages", "bytes": nbytes,
+                                 "l2": "1.2 GB moved per launch, larger than L2"},
+                      "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                   "frac": round(gbs / peak, 4), "traffic": None, "peak_source": src}}))
+
+
 def main():
     a = parse()
+    if a.workload != "decode":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        torch.cuda.set_device(0)
+        (run_cfg3 if a.workload == "cfg3" else run_copy)(a, torch.device("cuda", 0))
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -197,7 +197,7 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
 // scratch. The caller's scratch is cut into regions used in rotation; the launch that wraps around
 // to region 0 is a plain launch (it waits for everything before it), so a region is never reused
 // while an earlier launch could still touch it.
-constexpr int kMaxRegions = 16;
+constexpr int kMaxRegions = 64;
 struct ScratchTurn {
   const void* key;
   unsigned count;
@@ -269,9 +269,15 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
 int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks) {
   (void)max_blocks;  // the split count follows the SM count, not the context length
   if (max_decode <= 0 || n_heads_local <= 0) return 0;
-  // partials of (sequences + CTAs) segments plus the arrival counters, for one launch of at most
-  // 512 sequences on at most 512 CTAs; sixteen such regions so that independent launches can rotate
-  return 16 * ((decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL);
+  // One region holds the partials of (sequences + CTAs) segments plus the arrival counters of a
+  // launch of at most 512 sequences on at most 512 CTAs. Independent launches rotate through
+  // regions; re-entering the first one is a sync point whose cost is shared by all regions, so
+  // give as many as fit in about 128 Ki slots (64 MiB of pa), at least 16, at most 64.
+  const long long one = (decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL;
+  long long regions = (128 * 1024) / one;
+  if (regions < 16) regions = 16;
+  if (regions > kMaxRegions) regions = kMaxRegions;
+  return regions * one;
 }
 
 int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -329,8 +335,8 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
       P.partial_slots = need;
       P.independent = 1;
       // The launch that re-enters region 0 waits for all earlier kernels before it lets the next
-      // launch start (sync_first): a region is reused 16 launches later, and between any launch and
-      // the one 16 before it lies such a sync point, so the earlier user has always completed.
+      // launch start (sync_first): a region is reused one full rotation later, and between any launch and
+      // its region's previous user lies such a sync point, so the earlier user has always completed.
       P.sync_first = region == 0 ? 1 : 0;
       const bool pdl = true;
       for (int base = 0; base < n_kv;) {

@@ -116,7 +116,7 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
  * the start of the step, engine/src/model_runtime.cu:295-302).
  *   FQB_DECODE_INDEPENDENT  the caller states that the kernel launched immediately before this call
  *       writes NOTHING this call reads (q, cache, metadata) and does not read `out`. The launch then
- *       streams KV while that kernel is still running; consecutive calls rotate through up to 16
+ *       streams KV while that kernel is still running; consecutive calls rotate through up to 64
  *       regions of the scratch and the launch that re-enters the first region completes all earlier
  *       work before any later launch may start, so scratch is never shared by two live launches. Meant for back-to-back attention over independent
  *       caches (micro-batches, benchmarks); without the flag the call is always safe. */
