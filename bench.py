@@ -41,7 +41,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch from the ncu
 # capture summarised under profiles/ (bytes per launch at the workload's full size), or None.
-NCU_TRAFFIC_BYTES = {"cfg2": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 556_570_368}
 
 
 def parse():

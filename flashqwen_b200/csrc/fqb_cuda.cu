@@ -14,6 +14,7 @@
 #include "errors.h"
 #include "kv_append.cuh"
 #include "prefill.cuh"
+#include "prefill_tc.cuh"
 
 namespace fqb {
 namespace {
@@ -76,17 +77,21 @@ int get_encode(EncodeFn& fn) {
   return FQB_OK;
 }
 
-int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtensorMap& map) {
+// half_boxes = false: box {64,16,2,2,1} = one 8 KiB page slice (K and V, both halves) per load.
+// half_boxes = true : box {64,16,1,1,1} = one 2 KiB half of one plane, so that the caller can place
+//                     the pieces as a UMMA operand tile.
+int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtensorMap& map, bool half_boxes = false) {
   struct Entry {
     const void* ptr;
     int nb, kvh;
+    bool half;
     CUtensorMap map;
   };
   constexpr int kCache = 128;
   static thread_local Entry lru[kCache];
   static thread_local int used = 0, next = 0;
   for (int i = 0; i < used; ++i)
-    if (lru[i].ptr == cache && lru[i].nb == num_blocks && lru[i].kvh == kv_heads_local) {
+    if (lru[i].ptr == cache && lru[i].nb == num_blocks && lru[i].kvh == kv_heads_local && lru[i].half == half_boxes) {
       map = lru[i].map;
       return FQB_OK;
     }
@@ -96,7 +101,7 @@ int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtens
   cuuint64_t dims[5] = {64, static_cast<cuuint64_t>(kTok), static_cast<cuuint64_t>(kv_heads_local) * 2, 2,
                         static_cast<cuuint64_t>(num_blocks)};
   cuuint64_t strides[4] = {row_bytes, 128, row_bytes * kTok, row_bytes * kTok * 2};
-  cuuint32_t box[5] = {64, static_cast<cuuint32_t>(kTok), 2, 2, 1};
+  cuuint32_t box[5] = {64, static_cast<cuuint32_t>(kTok), half_boxes ? 1u : 2u, half_boxes ? 1u : 2u, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -107,6 +112,7 @@ int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtens
   e.ptr = cache;
   e.nb = num_blocks;
   e.kvh = kv_heads_local;
+  e.half = half_boxes;
   e.map = map;
   next = (next + 1) % kCache;
   if (used < kCache) ++used;
@@ -442,8 +448,11 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
       (q_stride % 2))
     return set_error(FQB_ERR_INVALID, "attn_prefill: misaligned pointer or stride");
   if (n_kv > 65535 || R > 65535) return set_error(FQB_ERR_SHAPE, "attn_prefill: n_kv or R above 65535");
+  // FQB_PREFILL=mma selects the mma.sync kernel (kept for comparison); the default is the tcgen05 one
+  const char* sel = std::getenv("FQB_PREFILL");
+  const bool use_tc = !(sel && sel[0] == 'm');
   CUtensorMap map;
-  if (int rc = make_cache_map(cache, num_blocks, n_kv, map)) return rc;
+  if (int rc = make_cache_map(cache, num_blocks, n_kv, map, use_tc)) return rc;
   PrefillParams P;
   P.q = static_cast<const __nv_bfloat16*>(q);
   P.q_stride = q_stride;
@@ -458,12 +467,25 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   P.max_blocks = max_blocks;
   P.num_blocks = num_blocks;
   P.scale_log2 = scale * kLog2e;
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  if (use_tc) {
+    if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
+      return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
+    static thread_local int attr_dev_tc = -1;
+    if (attr_dev_tc != dev) {
+      FQB_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem::kAlloc));
+      attr_dev_tc = dev;
+    }
+    dim3 grid((max_qlen + kTcBM - 1) / kTcBM, n_kv, R);
+    prefill_tc_kernel<<<grid, kTcThreads, TcSmem::kAlloc, static_cast<cudaStream_t>(stream)>>>(map, P);
+    FQB_CUDA_TRY(cudaGetLastError());
+    return FQB_OK;
+  }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;
   auto kern = prefill_kernel<RT, NS, MINB>;
   static thread_local int attr_dev = -1;
-  int dev = 0;
-  FQB_CUDA_TRY(cudaGetDevice(&dev));
   if (attr_dev != dev) {
     FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     attr_dev = dev;

@@ -1,0 +1,369 @@
+// Kernel 3, Blackwell tensor-core version: chunked-prefill paged attention on tcgen05 / TMEM.
+//
+// Same operator as prefill_kernel (semantics of the reference's CutePrefillKernel,
+// engine/src/attn_cute.cu:30-147 of the FlashQwen tree). One CTA = 32 query rows x the 4 query
+// heads of one kv head = a 128-row MMA tile (row = head * 32 + query row); keys are consumed 64 at
+// a time (4 pages).
+//
+//   warp 4      TMA producer: per page and plane two 2 KiB boxes (one per 64-dim half) placed so
+//               that a 64-key K tile / V tile is a canonical 128-byte-swizzled UMMA operand
+//               ([half][key][64 dims], 8-key groups 1024 bytes apart); 3-stage ring.
+//   warp 5      one thread issues tcgen05.mma: S = Q K^T (M128 N64, 8 k-steps of 16 dims, both
+//               operands K-major) into one of two 64-column TMEM buffers, and O += P V
+//               (M128 N128, 4 k-steps of 16 keys, P K-major from shared memory, V MN-major) into
+//               a 128-column TMEM accumulator. S of tile k+1 is issued before PV of tile k, so the
+//               tensor pipe works while the softmax of tile k runs.
+//   warps 0-3   softmax: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, scale,
+//               causal mask, running max without any shuffle, exp2, P -> bf16 into shared memory.
+//               The accumulator is rescaled in TMEM only when a row's max grew by more than 2^8
+//               since the scale in use (the probabilities stay exact relative to that scale).
+// Completion is tracked with mbarriers (tcgen05.commit for MMA groups); every wait is bounded and
+// ends in a status code. TMEM (256 columns) is allocated by warp 5 and freed before exit.
+#pragma once
+
+#include "common.cuh"
+#include "prefill.cuh"
+
+namespace fqb {
+
+constexpr int kTcBM = 32;        // query rows per CTA
+constexpr int kTcBN = 64;        // keys per tile
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 192;
+constexpr int kTcCols = 256;     // TMEM columns: S0 [0,64), S1 [64,128), O [128,256)
+
+struct TcSmem {
+  static constexpr int kQ = 0;                                   // [2 k-blocks][128 rows][128 B]
+  static constexpr int kKV = 32768;                              // stages x {K 16 KiB, V 16 KiB}
+  static constexpr int kStage = 32768;
+  static constexpr int kP = kKV + kTcStages * kStage;            // [128 rows][128 B]
+  static constexpr int kBars = kP + 16384;
+  static constexpr int kTmemSlot = kBars + 16 * 8;
+  static constexpr int kTotal = kTmemSlot + 16;
+  static constexpr int kAlloc = kTotal + 1024;
+};
+
+// ---- UMMA descriptors -----------------------------------------------------------------------------
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets
+// in 16-byte units, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, A K-major, B K- or MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+          taddr),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 4-D tiled load of a 2 KiB box {64 dims, 16 tokens, 1 half, 1 plane, 1 block}
+__device__ __forceinline__ void tma_load_half(void* dst, const CUtensorMap* m, uint64_t* bar, int half, int plane,
+                                              int blk) {
+  tma_load_page(dst, m, bar, 0, 0, half, plane, blk);
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) {
+  using L = TcSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint64_t* kv_full = bars;               // [3]  producer -> MMA (tx bytes)
+  uint64_t* kv_empty = bars + 3;          // [3]  MMA commit -> producer
+  uint64_t* s_full = bars + 6;            // [2]  MMA commit -> softmax
+  uint64_t* s_free = bars + 8;            // [2]  softmax (128) -> MMA
+  uint64_t* p_full = bars + 10;           //      softmax (128) -> MMA
+  uint64_t* o_done = bars + 11;           //      MMA commit -> softmax
+  uint64_t* q_full = bars + 12;           //      softmax (128) -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+
+  const int r = P.rids[blockIdx.z];
+  const int kvh = blockIdx.y;
+  const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
+  const int ql = P.qlen[r], qs = P.qstart[r];
+  const int q0 = qtile * kTcBM;
+  if (q0 >= ql) return;  // before any allocation; the whole CTA leaves together
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTcCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    tma_prefetch_desc(&tmap);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    mbar_init(q_full, 128);
+    mbar_fence_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int qlast = min(q0 + kTcBM, ql) - 1;
+  int last_pos = P.pos[qs + qlast];
+  if (last_pos >= P.max_blocks * kTok) {
+    if (tid == 0) report(FQB_ERR_INDEX, kKidPrefill, last_pos);
+    last_pos = P.max_blocks * kTok - 1;
+  }
+  const int npages = last_pos / kTok + 1;             // <= 0 when last_pos < 0
+  const int ntiles = (last_pos + kTcBN) / kTcBN;      // ceil((last_pos + 1) / 64)
+  bool dead = false;
+  auto wait = [&](uint64_t* bar, uint32_t parity, int what) {
+    if (!dead && !mbar_wait_bounded(bar, parity)) {
+      dead = true;
+      report(FQB_ERR_TIMEOUT, kKidPrefill, what);
+    }
+  };
+  const uint32_t q_base = smem_u32(smem + L::kQ), p_base = smem_u32(smem + L::kP);
+
+  if (warp < 4) {
+    // =========================== softmax warps: one thread per MMA row ===========================
+    const int row = tid;                 // MMA row = head * 32 + query row
+    const int g = warp, qi = lane;
+    const int qrow = q0 + qi;
+    const bool valid = qrow < ql;
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(
+          P.q + static_cast<long long>(qs + (valid ? qrow : q0)) * P.q_stride + (kvh * kGroup + g) * kHd);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const uint4 v = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(smem + L::kQ + (c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+      }
+    }
+    proxy_fence_async();
+    mbar_arrive(q_full);
+    const int qp = valid ? P.pos[qs + qrow] : -1;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    float m_used = kNegBig, l = 0.f;
+
+#pragma unroll 1
+    for (int k = 0; k < ntiles; ++k) {
+      const int b = k & 1;
+      wait(&s_full[b], (k >> 1) & 1, k);
+      tc_fence_after();
+      float x[kTcBN];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_free[b]);
+      const int k0 = k * kTcBN;
+      float mx = kNegBig;
+      if (k0 + kTcBN - 1 > qp) {  // the tile crosses this row's causal edge (or lies beyond it)
+#pragma unroll
+        for (int j = 0; j < kTcBN; ++j) {
+          x[j] = (k0 + j <= qp) ? x[j] * P.scale_log2 : kNegBig;
+          mx = fmaxf(mx, x[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kTcBN; ++j) {
+          x[j] *= P.scale_log2;
+          mx = fmaxf(mx, x[j]);
+        }
+      }
+      const float m_new = fmaxf(m_used, mx);
+      const bool grow = m_new > m_used + 8.f;  // keep the scale in use unless the max moved by > 2^8
+      const float f = grow ? fast_exp2(m_used - m_new) : 1.f;
+      if (grow) {
+        m_used = m_new;
+        l *= f;
+      }
+      float sum = 0.f;
+      uint32_t pk[kTcBN / 2];
+#pragma unroll
+      for (int j = 0; j < kTcBN; j += 2) {
+        const float p0 = fast_exp2(x[j] - m_used), p1 = fast_exp2(x[j + 1] - m_used);
+        sum += p0 + p1;
+        pk[j >> 1] = pack_bf16(p0, p1);
+      }
+      l += sum;
+      if (k > 0) {
+        wait(o_done, (k - 1) & 1, 1000 + k);  // PV of the tile before has finished: P and O are ours
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            float o[16];
+            tmem_ld16(lane_addr + 128 + c * 16, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] *= f;
+            tmem_st16(lane_addr + 128 + c * 16, o);
+          }
+          tmem_wait_st();
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(smem + L::kP + row * 128 + ((c ^ (row & 7)) << 4)) =
+            make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+      if (k == ntiles - 1) {
+        // key slots past the chunk's last position (never written, or pages that do not exist):
+        // clear their V rows so that 0 * garbage cannot reach the accumulator
+        const int nvalid = last_pos - k0 + 1;
+        uint8_t* vst = smem + L::kKV + (k % kTcStages) * L::kStage + 16384;
+        for (int idx = tid; idx < (kTcBN - nvalid) * 16; idx += 128) {
+          const int vr = nvalid + (idx >> 4), c = idx & 15;
+          *reinterpret_cast<uint4*>(vst + (c >> 3) * 8192 + vr * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      proxy_fence_async();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> bf16 -> out ----
+    if (ntiles > 0) {
+      wait(o_done, (ntiles - 1) & 1, 2000);
+      tc_fence_after();
+    }
+    const float inv = (l > 0.f && ntiles > 0) ? 1.f / l : 0.f;
+    __nv_bfloat16* orow = P.out + (static_cast<long long>(qs + qrow) * P.n_heads + kvh * kGroup + g) * kHd;
+#pragma unroll 1
+    for (int c = 0; c < 8; ++c) {
+      float o[16];
+      if (ntiles > 0) {
+        tmem_ld16(lane_addr + 128 + c * 16, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = 0.f;
+      }
+      if (valid) {
+        uint4 a, bq;
+        a.x = pack_bf16(o[0] * inv, o[1] * inv);   a.y = pack_bf16(o[2] * inv, o[3] * inv);
+        a.z = pack_bf16(o[4] * inv, o[5] * inv);   a.w = pack_bf16(o[6] * inv, o[7] * inv);
+        bq.x = pack_bf16(o[8] * inv, o[9] * inv);  bq.y = pack_bf16(o[10] * inv, o[11] * inv);
+        bq.z = pack_bf16(o[12] * inv, o[13] * inv); bq.w = pack_bf16(o[14] * inv, o[15] * inv);
+        *reinterpret_cast<uint4*>(orow + c * 16) = a;
+        *reinterpret_cast<uint4*>(orow + c * 16 + 8) = bq;
+      }
+    }
+    tc_fence_before();
+  } else if (warp == 4) {
+    // =========================== TMA producer ===========================
+    const int* btr = P.bt + static_cast<long long>(r) * P.max_blocks;
+#pragma unroll 1
+    for (int k = 0; k < ntiles; ++k) {
+      const int stage = k % kTcStages;
+      const int pg0 = k * 4;
+      const int npg = min(4, npages - pg0);
+      const int mine = lane < npg ? __ldg(btr + pg0 + lane) : 0;
+      if (k >= kTcStages) wait(&kv_empty[stage], ((k / kTcStages) - 1) & 1, 3000 + k);
+      if (lane < npg && static_cast<unsigned>(mine) >= static_cast<unsigned>(P.num_blocks))
+        report(FQB_ERR_INDEX, kKidPrefill, mine);  // the loads below then read zeros
+      uint8_t* st = smem + L::kKV + stage * L::kStage;
+      if (lane == 0) mbar_expect_tx(&kv_full[stage], static_cast<uint32_t>(npg) * kPageBytes);
+      __syncwarp();
+      if (lane < npg) {
+#pragma unroll
+        for (int plane = 0; plane < 2; ++plane)
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+            tma_load_half(st + plane * 16384 + half * 8192 + lane * 2048, &tmap, &kv_full[stage], kvh * 2 + half,
+                          plane, mine);
+      }
+    }
+  } else {
+    // =========================== MMA issuer (one thread) ===========================
+    if (lane == 0) {
+      constexpr uint32_t kIdescS = umma_idesc(128, kTcBN, false);
+      constexpr uint32_t kIdescO = umma_idesc(128, kHd, true);
+      wait(q_full, 0, 4000);
+      tc_fence_after();
+#pragma unroll 1
+      for (int k = 0; k <= ntiles; ++k) {
+        if (k < ntiles) {
+          const int stage = k % kTcStages, b = k & 1;
+          wait(&kv_full[stage], (k / kTcStages) & 1, 5000 + k);
+          if (k >= 2) wait(&s_free[b], ((k >> 1) - 1) & 1, 6000 + k);
+          tc_fence_after();
+          const uint32_t kst = smem_u32(smem + L::kKV + stage * L::kStage);
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              umma_bf16(tmem + b * 64, umma_desc(q_base + kb * 16384 + j * 32, 16, 1024),
+                        umma_desc(kst + kb * 8192 + j * 32, 16, 1024), kIdescS, (kb | j) ? 1u : 0u);
+          umma_commit(&s_full[b]);
+        }
+        if (k >= 1) {
+          const int t = k - 1, stage = t % kTcStages;
+          wait(p_full, t & 1, 7000 + t);
+          tc_fence_after();
+          const uint32_t vst = smem_u32(smem + L::kKV + stage * L::kStage + 16384);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            umma_bf16(tmem + 128, umma_desc(p_base + j * 32, 16, 1024), umma_desc(vst + j * 2048, 8192, 1024),
+                      kIdescO, (t | j) ? 1u : 0u);
+          umma_commit(o_done);
+          umma_commit(&kv_empty[stage]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcCols) : "memory");
+  }
+}
+
+}  // namespace fqb
