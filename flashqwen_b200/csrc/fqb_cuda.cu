@@ -472,15 +472,43 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   if (use_tc) {
     if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
       return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
-    static thread_local int attr_dev_tc = -1;
-    if (attr_dev_tc != dev) {
-      FQB_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem::kAlloc));
-      attr_dev_tc = dev;
-    }
     dim3 grid((max_qlen + kTcBM - 1) / kTcBM, n_kv, R);
-    prefill_tc_kernel<<<grid, kTcThreads, TcSmem::kAlloc, static_cast<cudaStream_t>(stream)>>>(map, P);
-    FQB_CUDA_TRY(cudaGetLastError());
-    return FQB_OK;
+    // FQB_PREFILL_TC=32|22|21 picks stages x CTAs per SM (tuning aid)
+    const char* v = std::getenv("FQB_PREFILL_TC");
+    const int variant = v ? std::atoi(v) : 31;
+    auto go = [&](auto kern, int smem) -> int {
+      FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+      if (std::getenv("FQB_DEBUG_OCC")) {
+        int nb = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, kTcThreads, smem);
+        std::fprintf(stderr, "[fqb] prefill_tc variant %d: %d B dynamic smem, %d CTAs per SM\n", variant, smem, nb);
+        static bool once = false;
+        if (!once) {
+          once = true;
+          cudaFuncAttributes fa;
+          cudaFuncGetAttributes(&fa, kern);
+          std::fprintf(stderr, "[fqb] attrs: regs %d static smem %zu maxdyn %d maxthreads %d carveout %d\n", fa.numRegs,
+                       fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock,
+                       fa.preferredShmemCarveout);
+          for (int th = 128; th <= 256; th += 64) {
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, th, 64 * 1024);
+            std::fprintf(stderr, "[fqb] occupancy probe: %d threads 64 KiB -> %d CTAs per SM\n", th, nb);
+          }
+          for (int kb = 100; kb <= 114; ++kb) {
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, kTcThreads, kb * 1024);
+            std::fprintf(stderr, "[fqb] occupancy probe: %d KiB -> %d CTAs per SM\n", kb, nb);
+          }
+        }
+      }
+      kern<<<grid, kTcThreads, smem, static_cast<cudaStream_t>(stream)>>>(map, P);
+      FQB_CUDA_TRY(cudaGetLastError());
+      return FQB_OK;
+    };
+    if (variant == 22) return go(prefill_tc_kernel<2, 2>, TcSmem<2>::kAlloc);
+    if (variant == 21) return go(prefill_tc_kernel<2, 1>, TcSmem<2>::kAlloc);
+    if (variant == 41) return go(prefill_tc_kernel<4, 1>, TcSmem<4>::kAlloc);
+    return go(prefill_tc_kernel<3, 1>, TcSmem<3>::kAlloc);
   }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;

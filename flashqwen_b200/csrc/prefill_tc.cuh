@@ -7,7 +7,7 @@
 //
 //   warp 4      TMA producer: per page and plane two 2 KiB boxes (one per 64-dim half) placed so
 //               that a 64-key K tile / V tile is a canonical 128-byte-swizzled UMMA operand
-//               ([half][key][64 dims], 8-key groups 1024 bytes apart); 3-stage ring.
+//               ([half][key][64 dims], 8-key groups 1024 bytes apart); 2-stage ring, two CTAs per SM.
 //   warp 5      one thread issues tcgen05.mma: S = Q K^T (M128 N64, 8 k-steps of 16 dims, both
 //               operands K-major) into one of two 64-column TMEM buffers, and O += P V
 //               (M128 N128, 4 k-steps of 16 keys, P K-major from shared memory, V MN-major) into
@@ -18,7 +18,8 @@
 //               The accumulator is rescaled in TMEM only when a row's max grew by more than 2^8
 //               since the scale in use (the probabilities stay exact relative to that scale).
 // Completion is tracked with mbarriers (tcgen05.commit for MMA groups); every wait is bounded and
-// ends in a status code. TMEM (256 columns) is allocated by warp 5 and freed before exit.
+// ends in a status code. TMEM (256 columns per CTA, two CTAs per SM use all 512) is allocated by
+// warp 5 and freed before exit.
 #pragma once
 
 #include "common.cuh"
@@ -28,19 +29,19 @@ namespace fqb {
 
 constexpr int kTcBM = 32;        // query rows per CTA
 constexpr int kTcBN = 64;        // keys per tile
-constexpr int kTcStages = 3;
 constexpr int kTcThreads = 192;
 constexpr int kTcCols = 256;     // TMEM columns: S0 [0,64), S1 [64,128), O [128,256)
 
+template <int STAGES>
 struct TcSmem {
   static constexpr int kQ = 0;                                   // [2 k-blocks][128 rows][128 B]
   static constexpr int kKV = 32768;                              // stages x {K 16 KiB, V 16 KiB}
   static constexpr int kStage = 32768;
-  static constexpr int kP = kKV + kTcStages * kStage;            // [128 rows][128 B]
+  static constexpr int kP = kKV + STAGES * kStage;            // [128 rows][128 B]
   static constexpr int kBars = kP + 16384;
   static constexpr int kTmemSlot = kBars + 16 * 8;
   static constexpr int kTotal = kTmemSlot + 16;
-  static constexpr int kAlloc = kTotal + 1024;
+  static constexpr int kAlloc = kTotal;  // no alignment slack: two CTAs must fit one SM (see the check in the kernel)
 };
 
 // ---- UMMA descriptors -----------------------------------------------------------------------------
@@ -104,20 +105,26 @@ __device__ __forceinline__ void tma_load_half(void* dst, const CUtensorMap* m, u
   tma_load_page(dst, m, bar, 0, 0, half, plane, blk);
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1)
+template <int STAGES, int MINB>
+__global__ void __launch_bounds__(kTcThreads, MINB)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) {
-  using L = TcSmem;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  using L = TcSmem<STAGES>;
+  constexpr int kTcStages = STAGES;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) report(FQB_ERR_INVALID, kKidPrefill, static_cast<int>(smem_u32(smem)));
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-  uint64_t* kv_full = bars;               // [3]  producer -> MMA (tx bytes)
-  uint64_t* kv_empty = bars + 3;          // [3]  MMA commit -> producer
-  uint64_t* s_full = bars + 6;            // [2]  MMA commit -> softmax
-  uint64_t* s_free = bars + 8;            // [2]  softmax (128) -> MMA
-  uint64_t* p_full = bars + 10;           //      softmax (128) -> MMA
-  uint64_t* o_done = bars + 11;           //      MMA commit -> softmax
-  uint64_t* q_full = bars + 12;           //      softmax (128) -> MMA
+  static_assert(STAGES >= 2 && STAGES <= 4, "the barrier block below has room for 4 stages");
+  uint64_t* kv_full = bars;               // [4]  producer -> MMA (tx bytes)
+  uint64_t* kv_empty = bars + 4;          // [4]  MMA commit -> producer
+  uint64_t* s_full = bars + 8;            // [2]  MMA commit -> softmax
+  uint64_t* s_free = bars + 10;           // [2]  softmax (128) -> MMA
+  uint64_t* p_full = bars + 12;           //      softmax (128) -> MMA
+  uint64_t* o_done = bars + 13;           //      MMA commit -> softmax
+  uint64_t* q_full = bars + 14;           //      softmax (128) -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
   const int r = P.rids[blockIdx.z];
@@ -130,13 +137,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
 
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(kTcCols)
+                 "n"(kTcCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     tma_prefetch_desc(&tmap);
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < kTcStages; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
@@ -204,20 +211,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       tc_fence_before();
       mbar_arrive(&s_free[b]);
       const int k0 = k * kTcBN;
-      float mx = kNegBig;
       if (k0 + kTcBN - 1 > qp) {  // the tile crosses this row's causal edge (or lies beyond it)
 #pragma unroll
-        for (int j = 0; j < kTcBN; ++j) {
-          x[j] = (k0 + j <= qp) ? x[j] * P.scale_log2 : kNegBig;
-          mx = fmaxf(mx, x[j]);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < kTcBN; ++j) {
-          x[j] *= P.scale_log2;
-          mx = fmaxf(mx, x[j]);
-        }
+        for (int j = 0; j < kTcBN; ++j)
+          if (k0 + j > qp) x[j] = kNegBig;
       }
+      // four independent chains each for the max and for the sum: a single warp per scheduler has
+      // nothing else to hide the dependent-issue latency of one long chain
+      float mx0 = kNegBig, mx1 = kNegBig, mx2 = kNegBig, mx3 = kNegBig;
+#pragma unroll
+      for (int j = 0; j < kTcBN; j += 4) {
+        mx0 = fmaxf(mx0, x[j]);
+        mx1 = fmaxf(mx1, x[j + 1]);
+        mx2 = fmaxf(mx2, x[j + 2]);
+        mx3 = fmaxf(mx3, x[j + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2;  // scale > 0: max commutes
       const float m_new = fmaxf(m_used, mx);
       const bool grow = m_new > m_used + 8.f;  // keep the scale in use unless the max moved by > 2^8
       const float f = grow ? fast_exp2(m_used - m_new) : 1.f;
@@ -225,14 +234,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
         m_used = m_new;
         l *= f;
       }
-      float sum = 0.f;
+      float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
       uint32_t pk[kTcBN / 2];
+      const float neg_m = -m_used;
 #pragma unroll
-      for (int j = 0; j < kTcBN; j += 2) {
-        const float p0 = fast_exp2(x[j] - m_used), p1 = fast_exp2(x[j + 1] - m_used);
-        sum += p0 + p1;
+      for (int j = 0; j < kTcBN; j += 4) {
+        const float p0 = fast_exp2(fmaf(x[j], P.scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(x[j + 1], P.scale_log2, neg_m));
+        const float p2 = fast_exp2(fmaf(x[j + 2], P.scale_log2, neg_m));
+        const float p3 = fast_exp2(fmaf(x[j + 3], P.scale_log2, neg_m));
+        sm0 += p0; sm1 += p1; sm2 += p2; sm3 += p3;
         pk[j >> 1] = pack_bf16(p0, p1);
+        pk[(j >> 1) + 1] = pack_bf16(p2, p3);
       }
+      const float sum = (sm0 + sm1) + (sm2 + sm3);
       l += sum;
       if (k > 0) {
         wait(o_done, (k - 1) & 1, 1000 + k);  // PV of the tile before has finished: P and O are ours
@@ -362,7 +377,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTcCols) : "memory");
   }
 }
 
