@@ -467,48 +467,26 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   P.max_blocks = max_blocks;
   P.num_blocks = num_blocks;
   P.scale_log2 = scale * kLog2e;
+  P.dbg = std::getenv("FQB_PREFILL_DBG") ? std::atoi(std::getenv("FQB_PREFILL_DBG")) : 0;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
   if (use_tc) {
     if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
       return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
-    dim3 grid((max_qlen + kTcBM - 1) / kTcBM, n_kv, R);
-    // FQB_PREFILL_TC=32|22|21 picks stages x CTAs per SM (tuning aid)
+    // FQB_PREFILL_TC=<groups><stages> picks row groups per CTA and K/V stages (tuning aid); default 23
     const char* v = std::getenv("FQB_PREFILL_TC");
-    const int variant = v ? std::atoi(v) : 31;
-    auto go = [&](auto kern, int smem) -> int {
+    const int variant = v ? std::atoi(v) : 23;
+    auto go = [&](auto kern, int smem, int threads, int rows) -> int {
       FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-      if (std::getenv("FQB_DEBUG_OCC")) {
-        int nb = -1;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, kTcThreads, smem);
-        std::fprintf(stderr, "[fqb] prefill_tc variant %d: %d B dynamic smem, %d CTAs per SM\n", variant, smem, nb);
-        static bool once = false;
-        if (!once) {
-          once = true;
-          cudaFuncAttributes fa;
-          cudaFuncGetAttributes(&fa, kern);
-          std::fprintf(stderr, "[fqb] attrs: regs %d static smem %zu maxdyn %d maxthreads %d carveout %d\n", fa.numRegs,
-                       fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock,
-                       fa.preferredShmemCarveout);
-          for (int th = 128; th <= 256; th += 64) {
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, th, 64 * 1024);
-            std::fprintf(stderr, "[fqb] occupancy probe: %d threads 64 KiB -> %d CTAs per SM\n", th, nb);
-          }
-          for (int kb = 100; kb <= 114; ++kb) {
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, kTcThreads, kb * 1024);
-            std::fprintf(stderr, "[fqb] occupancy probe: %d KiB -> %d CTAs per SM\n", kb, nb);
-          }
-        }
-      }
-      kern<<<grid, kTcThreads, smem, static_cast<cudaStream_t>(stream)>>>(map, P);
+      dim3 grid((max_qlen + rows - 1) / rows, n_kv, R);
+      kern<<<grid, threads, smem, static_cast<cudaStream_t>(stream)>>>(map, P);
       FQB_CUDA_TRY(cudaGetLastError());
       return FQB_OK;
     };
-    if (variant == 22) return go(prefill_tc_kernel<2, 2>, TcSmem<2>::kAlloc);
-    if (variant == 21) return go(prefill_tc_kernel<2, 1>, TcSmem<2>::kAlloc);
-    if (variant == 41) return go(prefill_tc_kernel<4, 1>, TcSmem<4>::kAlloc);
-    return go(prefill_tc_kernel<3, 1>, TcSmem<3>::kAlloc);
+    if (variant == 13) return go(prefill_tc_kernel<1, 3>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32);
+    if (variant == 14) return go(prefill_tc_kernel<1, 4>, TcSmem<1, 4>::kAlloc, TcSmem<1, 4>::kThreads, 32);
+    if (variant == 22) return go(prefill_tc_kernel<2, 2>, TcSmem<2, 2>::kAlloc, TcSmem<2, 2>::kThreads, 64);
+    return go(prefill_tc_kernel<2, 3>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
   }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;
@@ -576,6 +554,11 @@ int fqb_device_status(int32_t* detail) {
   if (detail) std::memcpy(detail, h, sizeof(h));
   if (h[0] != 0)
     return set_error(h[0], "device status: code %d from kernel %d, block %d, value %d", h[0], h[1], h[2], h[3]);
+  return FQB_OK;
+}
+
+int fqb_debug_tc_timeline(long long* out, int n) {
+  FQB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof(long long) * (n < 4096 ? n : 4096)));
   return FQB_OK;
 }
 

@@ -5,15 +5,17 @@
 // heads of one kv head = a 128-row MMA tile (row = head * 32 + query row); keys are consumed 64 at
 // a time (4 pages).
 //
-//   warp 4      TMA producer: per page and plane two 2 KiB boxes (one per 64-dim half) placed so
+//   TMA warp    producer: per page and plane two 2 KiB boxes (one per 64-dim half) placed so
 //               that a 64-key K tile / V tile is a canonical 128-byte-swizzled UMMA operand
 //               ([half][key][64 dims], 8-key groups 1024 bytes apart); 2-stage ring, two CTAs per SM.
-//   warp 5      one thread issues tcgen05.mma: S = Q K^T (M128 N64, 8 k-steps of 16 dims, both
+//   MMA warps   one thread of each issues tcgen05.mma: the first S = Q K^T (M128 N64, 8 k-steps of 16 dims, both
 //               operands K-major) into one of two 64-column TMEM buffers, and O += P V
 //               (M128 N128, 4 k-steps of 16 keys, P K-major from shared memory, V MN-major) into
-//               a 128-column TMEM accumulator. S of tile k+1 is issued before PV of tile k, so the
-//               tensor pipe works while the softmax of tile k runs.
-//   warps 0-3   softmax: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, scale,
+//               a 128-column TMEM accumulator (issued by the second warp). The S issuer runs up to
+//               two tiles ahead of the softmax, so the tensor pipe works while the softmax runs; all
+//               descriptors are built once, the issue loops only add k-step offsets.
+//   warps 0-3 (and 4-7 with two row groups per CTA)
+//               softmax: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, scale,
 //               causal mask, running max without any shuffle, exp2, P -> bf16 into shared memory.
 //               The accumulator is rescaled in TMEM only when a row's max grew by more than 2^8
 //               since the scale in use (the probabilities stay exact relative to that scale).
@@ -27,21 +29,28 @@
 
 namespace fqb {
 
-constexpr int kTcBM = 32;        // query rows per CTA
-constexpr int kTcBN = 64;        // keys per tile
-constexpr int kTcThreads = 192;
-constexpr int kTcCols = 256;     // TMEM columns: S0 [0,64), S1 [64,128), O [128,256)
+__device__ long long g_tc_dbg[4096];
+__device__ __forceinline__ void tc_stamp(int on, int slot) { if (on && slot < 4096) g_tc_dbg[slot] = clock64(); }
 
-template <int STAGES>
+constexpr int kTcGroupRows = 32;  // query rows per group (x 4 q heads = one 128-row MMA tile)
+constexpr int kTcBN = 64;         // keys per tile
+constexpr int kTcGroupCols = 256; // TMEM columns per group: S0 [0,64), S1 [64,128), O [128,256)
+
+// G = row groups per CTA (1 or 2): each group is a 128-row MMA tile with its own Q, P, S and O; the
+// groups share the K/V stages, so with G = 2 every K/V tile fetched from L2 feeds twice the math and
+// the softmax of one group overlaps the MMAs of the other.
+template <int G, int STAGES>
 struct TcSmem {
-  static constexpr int kQ = 0;                                   // [2 k-blocks][128 rows][128 B]
-  static constexpr int kKV = 32768;                              // stages x {K 16 KiB, V 16 KiB}
+  static constexpr int kQ = 0;                                   // G x [2 k-blocks][128 rows][128 B]
+  static constexpr int kKV = G * 32768;                          // stages x {K 16 KiB, V 16 KiB}
   static constexpr int kStage = 32768;
-  static constexpr int kP = kKV + STAGES * kStage;            // [128 rows][128 B]
-  static constexpr int kBars = kP + 16384;
-  static constexpr int kTmemSlot = kBars + 16 * 8;
+  static constexpr int kP = kKV + STAGES * kStage;               // G x 2 x [128 rows][128 B]
+  static constexpr int kBars = kP + G * 2 * 16384;
+  static constexpr int kTmemSlot = kBars + 32 * 8;
   static constexpr int kTotal = kTmemSlot + 16;
-  static constexpr int kAlloc = kTotal;  // no alignment slack: two CTAs must fit one SM (see the check in the kernel)
+  static constexpr int kAlloc = kTotal;                          // base must be 1024-byte aligned (checked)
+  static constexpr int kThreads = (4 * G + 3) * 32;              // softmax warps, TMA warp, two MMA-issue warps
+  static constexpr int kRows = G * kTcGroupRows;                 // query rows per CTA
 };
 
 // ---- UMMA descriptors -----------------------------------------------------------------------------
@@ -105,11 +114,13 @@ __device__ __forceinline__ void tma_load_half(void* dst, const CUtensorMap* m, u
   tma_load_page(dst, m, bar, 0, 0, half, plane, blk);
 }
 
-template <int STAGES, int MINB>
-__global__ void __launch_bounds__(kTcThreads, MINB)
+template <int G, int STAGES>
+__global__ void __launch_bounds__(TcSmem<G, STAGES>::kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) {
-  using L = TcSmem<STAGES>;
-  constexpr int kTcStages = STAGES;
+  using L = TcSmem<G, STAGES>;
+  static_assert(G >= 1 && G <= 2 && STAGES >= 2 && STAGES <= 4, "barrier block and TMEM are laid out for these");
+  constexpr int kCols = G * kTcGroupCols;
+  constexpr int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1, kPvWarp = 4 * G + 2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
@@ -117,43 +128,50 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-  static_assert(STAGES >= 2 && STAGES <= 4, "the barrier block below has room for 4 stages");
-  uint64_t* kv_full = bars;               // [4]  producer -> MMA (tx bytes)
-  uint64_t* kv_empty = bars + 4;          // [4]  MMA commit -> producer
-  uint64_t* s_full = bars + 8;            // [2]  MMA commit -> softmax
-  uint64_t* s_free = bars + 10;           // [2]  softmax (128) -> MMA
-  uint64_t* p_full = bars + 12;           //      softmax (128) -> MMA
-  uint64_t* o_done = bars + 13;           //      MMA commit -> softmax
-  uint64_t* q_full = bars + 14;           //      softmax (128) -> MMA
+  uint64_t* kv_full = bars;        // [4]  producer -> MMA (tx bytes)
+  uint64_t* kv_empty = bars + 4;   // [4]  MMA commit -> producer
+  // per group gi at bars + 8 + 10*gi: s_full[2] (MMA commit -> softmax), s_free[2] (softmax, 1 per warp ->
+  // MMA), p_full[2] (softmax, 1 per warp -> MMA), o_done[2] (MMA commit -> softmax), q_full. S, P and
+  // their barriers are double-buffered by tile parity, so the softmax of tile k+1 never waits for the
+  // MMA round trip of tile k (a single P buffer tied every tile to two cross-warp hand-offs).
+  auto s_full = [&](int gi, int b) { return bars + 8 + 10 * gi + b; };
+  auto s_free = [&](int gi, int b) { return bars + 8 + 10 * gi + 2 + b; };
+  auto p_full = [&](int gi, int b) { return bars + 8 + 10 * gi + 4 + b; };
+  auto o_done = [&](int gi, int b) { return bars + 8 + 10 * gi + 6 + b; };
+  auto q_full = [&](int gi) { return bars + 8 + 10 * gi + 8; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
   const int r = P.rids[blockIdx.z];
   const int kvh = blockIdx.y;
   const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
   const int ql = P.qlen[r], qs = P.qstart[r];
-  const int q0 = qtile * kTcBM;
+  const int q0 = qtile * L::kRows;
   if (q0 >= ql) return;  // before any allocation; the whole CTA leaves together
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "n"(kTcCols)
+                 "n"(kCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     tma_prefetch_desc(&tmap);
-    for (int i = 0; i < kTcStages; ++i) {
+    for (int i = 0; i < STAGES; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
+    for (int gi = 0; gi < G; ++gi) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full(gi, b), 1);
+        mbar_init(s_free(gi, b), 4);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(p_full(gi, b), 4);
+        mbar_init(o_done(gi, b), 1);
+      }
+      mbar_init(q_full(gi), 4);
     }
-    mbar_init(p_full, 128);
-    mbar_init(o_done, 1);
-    mbar_init(q_full, 128);
     mbar_fence_init();
   }
   tc_fence_before();
@@ -161,14 +179,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  const int qlast = min(q0 + kTcBM, ql) - 1;
-  int last_pos = P.pos[qs + qlast];
-  if (last_pos >= P.max_blocks * kTok) {
-    if (tid == 0) report(FQB_ERR_INDEX, kKidPrefill, last_pos);
-    last_pos = P.max_blocks * kTok - 1;
+  // Per group: last visible key position of its rows and the number of 64-key tiles it consumes.
+  // A later group has later rows, so the CTA loads max over the groups (pages up to cta_last).
+  int g_last[G], g_tiles[G];
+  int cta_last = -1;
+#pragma unroll
+  for (int gi = 0; gi < G; ++gi) {
+    const int first = q0 + gi * kTcGroupRows;
+    int lp = -1;
+    if (first < ql) {
+      lp = P.pos[qs + min(first + kTcGroupRows, ql) - 1];
+      if (lp >= P.max_blocks * kTok) {
+        if (tid == 0) report(FQB_ERR_INDEX, kKidPrefill, lp);
+        lp = P.max_blocks * kTok - 1;
+      }
+    }
+    g_last[gi] = lp;
+    g_tiles[gi] = lp < 0 ? 0 : lp / kTcBN + 1;
+    cta_last = max(cta_last, lp);
   }
-  const int npages = last_pos / kTok + 1;             // <= 0 when last_pos < 0
-  const int ntiles = (last_pos + kTcBN) / kTcBN;      // ceil((last_pos + 1) / 64)
+  const int npages = cta_last < 0 ? 0 : cta_last / kTok + 1;
+  const int ntiles = cta_last < 0 ? 0 : cta_last / kTcBN + 1;
+  const int stamp_on = (P.dbg & 256) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == gridDim.z - 1;
   bool dead = false;
   auto wait = [&](uint64_t* bar, uint32_t parity, int what) {
     if (!dead && !mbar_wait_bounded(bar, parity)) {
@@ -176,40 +208,51 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       report(FQB_ERR_TIMEOUT, kKidPrefill, what);
     }
   };
-  const uint32_t q_base = smem_u32(smem + L::kQ), p_base = smem_u32(smem + L::kP);
 
-  if (warp < 4) {
+  if (warp < 4 * G) {
     // =========================== softmax warps: one thread per MMA row ===========================
-    const int row = tid;                 // MMA row = head * 32 + query row
-    const int g = warp, qi = lane;
-    const int qrow = q0 + qi;
+    const int gi = warp >> 2;            // row group
+    const int row = tid & 127;           // MMA row inside the group = head * 32 + query row
+    const int g = warp & 3, qi = lane;
+    const int qrow = q0 + gi * kTcGroupRows + qi;
     const bool valid = qrow < ql;
+    uint8_t* q_smem = smem + L::kQ + gi * 32768;
+    uint8_t* p_group = smem + L::kP + gi * 2 * 16384;
+    const int my_tiles = g_tiles[gi];
     {
       const uint4* src = reinterpret_cast<const uint4*>(
           P.q + static_cast<long long>(qs + (valid ? qrow : q0)) * P.q_stride + (kvh * kGroup + g) * kHd);
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         const uint4 v = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(smem + L::kQ + (c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(q_smem + (c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
       }
     }
     proxy_fence_async();
-    mbar_arrive(q_full);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(q_full(gi));  // one arrival per warp: 128 arrivals on one word serialise
     const int qp = valid ? P.pos[qs + qrow] : -1;
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_addr = tmem + gi * kTcGroupCols + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     float m_used = kNegBig, l = 0.f;
 
 #pragma unroll 1
-    for (int k = 0; k < ntiles; ++k) {
+    for (int k = 0; k < my_tiles; ++k) {
       const int b = k & 1;
-      wait(&s_full[b], (k >> 1) & 1, k);
+      wait(s_full(gi, b), (k >> 1) & 1, k);
+      if (tid == 0 && k < 100) tc_stamp(stamp_on, k * 8 + 0);
       tc_fence_after();
       float x[kTcBN];
+      if (P.dbg & 8) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
-      tmem_wait_ld();
+        for (int j = 0; j < kTcBN; ++j) x[j] = static_cast<float>(j + k);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
+        tmem_wait_ld();
+      }
       tc_fence_before();
-      mbar_arrive(&s_free[b]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free(gi, b));
       const int k0 = k * kTcBN;
       if (k0 + kTcBN - 1 > qp) {  // the tile crosses this row's causal edge (or lies beyond it)
 #pragma unroll
@@ -237,6 +280,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
       uint32_t pk[kTcBN / 2];
       const float neg_m = -m_used;
+      if (P.dbg & 1) {
+#pragma unroll
+        for (int j = 0; j < kTcBN / 2; ++j) pk[j] = __float_as_uint(x[j]);
+      } else
 #pragma unroll
       for (int j = 0; j < kTcBN; j += 4) {
         const float p0 = fast_exp2(fmaf(x[j], P.scale_log2, neg_m));
@@ -247,53 +294,60 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
         pk[j >> 1] = pack_bf16(p0, p1);
         pk[(j >> 1) + 1] = pack_bf16(p2, p3);
       }
-      const float sum = (sm0 + sm1) + (sm2 + sm3);
-      l += sum;
-      if (k > 0) {
-        wait(o_done, (k - 1) & 1, 1000 + k);  // PV of the tile before has finished: P and O are ours
+      l += (sm0 + sm1) + (sm2 + sm3);
+      // O is touched only when some row of the warp moved its scale: then PV of the tile before must
+      // have finished. Otherwise only P[b] must be free again, i.e. PV of tile k-2 has finished.
+      const bool any_grow = k > 0 && __any_sync(0xffffffffu, grow);
+      if (any_grow) {
+        wait(o_done(gi, (k - 1) & 1), ((k - 1) >> 1) & 1, 1000 + k);
         tc_fence_after();
-        if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
-            float o[16];
-            tmem_ld16(lane_addr + 128 + c * 16, o);
-            tmem_wait_ld();
+        for (int c = 0; c < 8; ++c) {
+          float o[16];
+          tmem_ld16(lane_addr + 128 + c * 16, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] *= f;
-            tmem_st16(lane_addr + 128 + c * 16, o);
-          }
-          tmem_wait_st();
+          for (int i = 0; i < 16; ++i) o[i] *= f;
+          tmem_st16(lane_addr + 128 + c * 16, o);
         }
+        tmem_wait_st();
+      } else if (k >= 2) {
+        wait(o_done(gi, b), ((k - 2) >> 1) & 1, 1500 + k);
       }
+      uint8_t* p_smem = p_group + b * 16384;
+      if (!(P.dbg & 2))
 #pragma unroll
       for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(smem + L::kP + row * 128 + ((c ^ (row & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(p_smem + row * 128 + ((c ^ (row & 7)) << 4)) =
             make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
       if (k == ntiles - 1) {
-        // key slots past the chunk's last position (never written, or pages that do not exist):
-        // clear their V rows so that 0 * garbage cannot reach the accumulator
-        const int nvalid = last_pos - k0 + 1;
-        uint8_t* vst = smem + L::kKV + (k % kTcStages) * L::kStage + 16384;
-        for (int idx = tid; idx < (kTcBN - nvalid) * 16; idx += 128) {
+        // key slots past the CTA's last position (never written, or pages that do not exist): clear
+        // their V rows so that 0 * garbage cannot reach an accumulator. Keys between this group's
+        // and the CTA's last position are real data another group still needs; they stay.
+        const int nvalid = cta_last - k0 + 1;
+        uint8_t* vst = smem + L::kKV + (k % STAGES) * L::kStage + 16384;
+        for (int idx = row; idx < (kTcBN - nvalid) * 16; idx += 128) {
           const int vr = nvalid + (idx >> 4), c = idx & 15;
           *reinterpret_cast<uint4*>(vst + (c >> 3) * 8192 + vr * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      proxy_fence_async();
+      if (!(P.dbg & 4)) proxy_fence_async();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (tid == 0 && k < 100) tc_stamp(stamp_on, k * 8 + 1);
+      if (lane == 0) mbar_arrive(p_full(gi, b));
     }
     // ---- epilogue: O / l -> bf16 -> out ----
-    if (ntiles > 0) {
-      wait(o_done, (ntiles - 1) & 1, 2000);
+    if (my_tiles > 0) {
+      wait(o_done(gi, (my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1, 2000);
       tc_fence_after();
     }
-    const float inv = (l > 0.f && ntiles > 0) ? 1.f / l : 0.f;
+    const float inv = (l > 0.f && my_tiles > 0) ? 1.f / l : 0.f;
     __nv_bfloat16* orow = P.out + (static_cast<long long>(qs + qrow) * P.n_heads + kvh * kGroup + g) * kHd;
 #pragma unroll 1
     for (int c = 0; c < 8; ++c) {
       float o[16];
-      if (ntiles > 0) {
+      if (my_tiles > 0) {
         tmem_ld16(lane_addr + 128 + c * 16, o);
         tmem_wait_ld();
       } else {
@@ -311,16 +365,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       }
     }
     tc_fence_before();
-  } else if (warp == 4) {
+  } else if (warp == kProducerWarp) {
     // =========================== TMA producer ===========================
     const int* btr = P.bt + static_cast<long long>(r) * P.max_blocks;
 #pragma unroll 1
     for (int k = 0; k < ntiles; ++k) {
-      const int stage = k % kTcStages;
+      const int stage = k % STAGES;
       const int pg0 = k * 4;
-      const int npg = min(4, npages - pg0);
+      const int npg = (P.dbg & 64) ? 1 : min(4, npages - pg0);
       const int mine = lane < npg ? __ldg(btr + pg0 + lane) : 0;
-      if (k >= kTcStages) wait(&kv_empty[stage], ((k / kTcStages) - 1) & 1, 3000 + k);
+      if (k >= STAGES) wait(&kv_empty[stage], ((k / STAGES) - 1) & 1, 3000 + k);
       if (lane < npg && static_cast<unsigned>(mine) >= static_cast<unsigned>(P.num_blocks))
         report(FQB_ERR_INDEX, kKidPrefill, mine);  // the loads below then read zeros
       uint8_t* st = smem + L::kKV + stage * L::kStage;
@@ -335,49 +389,101 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
                           plane, mine);
       }
     }
-  } else {
-    // =========================== MMA issuer (one thread) ===========================
+  } else if (warp == kMmaWarp) {
+    // =========================== S = Q K^T issuer (one thread) ===========================
+    // Issuing is the hot loop of a single thread, so every descriptor is built once up front and
+    // the loop only adds the k-step offsets (16-byte units) to the low word.
     if (lane == 0) {
       constexpr uint32_t kIdescS = umma_idesc(128, kTcBN, false);
-      constexpr uint32_t kIdescO = umma_idesc(128, kHd, true);
-      wait(q_full, 0, 4000);
+      uint64_t qd[G], kd[STAGES];
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) qd[gi] = umma_desc(smem_u32(smem + L::kQ + gi * 32768), 16, 1024);
+#pragma unroll
+      for (int st = 0; st < STAGES; ++st) kd[st] = umma_desc(smem_u32(smem + L::kKV + st * L::kStage), 16, 1024);
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi)
+        if (g_tiles[gi] > 0) wait(q_full(gi), 0, 4000 + gi);
       tc_fence_after();
+      int stage = 0;
+      uint32_t kv_par = 0;
 #pragma unroll 1
-      for (int k = 0; k <= ntiles; ++k) {
-        if (k < ntiles) {
-          const int stage = k % kTcStages, b = k & 1;
-          wait(&kv_full[stage], (k / kTcStages) & 1, 5000 + k);
-          if (k >= 2) wait(&s_free[b], ((k >> 1) - 1) & 1, 6000 + k);
+      for (int k = 0; k < ntiles; ++k) {
+        const int b = k & 1;
+        if (k < 100) tc_stamp(stamp_on, k * 8 + 2);
+        wait(&kv_full[stage], kv_par, 5000 + k);
+        if (k < 100) tc_stamp(stamp_on, k * 8 + 3);
+        uint64_t kdesc = kd[0];
+#pragma unroll
+        for (int st = 1; st < STAGES; ++st) kdesc = stage == st ? kd[st] : kdesc;
+        // One group after the other: measured, a tcgen05.mma of these shapes costs about
+        // 80 + 0.55 * N clocks whether or not its neighbours are independent, and finishing one
+        // group's S early lets its softmax start while the other group's MMAs still issue.
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+          if (k >= g_tiles[gi]) continue;  // this group's rows cannot see the tile
+          if (k >= 2) wait(s_free(gi, b), ((k >> 1) - 1) & 1, 6000 + k);
           tc_fence_after();
-          const uint32_t kst = smem_u32(smem + L::kKV + stage * L::kStage);
+          const uint32_t d = tmem + gi * kTcGroupCols + b * 64;
 #pragma unroll
           for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              umma_bf16(tmem + b * 64, umma_desc(q_base + kb * 16384 + j * 32, 16, 1024),
-                        umma_desc(kst + kb * 8192 + j * 32, 16, 1024), kIdescS, (kb | j) ? 1u : 0u);
-          umma_commit(&s_full[b]);
+              umma_bf16(d, qd[gi] + ((kb * 16384 + j * 32) >> 4), kdesc + ((kb * 8192 + j * 32) >> 4), kIdescS,
+                        (kb | j) ? 1u : 0u);
+          umma_commit(s_full(gi, b));
+          if (k < 100 && gi == 0) tc_stamp(stamp_on, k * 8 + 4);
         }
-        if (k >= 1) {
-          const int t = k - 1, stage = t % kTcStages;
-          wait(p_full, t & 1, 7000 + t);
+        if (++stage == STAGES) {
+          stage = 0;
+          kv_par ^= 1u;
+        }
+      }
+    }
+    tc_fence_before();
+  } else {
+    // =========================== O += P V issuer (one thread) ===========================
+    if (lane == 0) {
+      constexpr uint32_t kIdescO = umma_idesc(128, kHd, true);
+      uint64_t pd[G][2], vd[STAGES];
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) pd[gi][b] = umma_desc(smem_u32(smem + L::kP + (gi * 2 + b) * 16384), 16, 1024);
+#pragma unroll
+      for (int st = 0; st < STAGES; ++st)
+        vd[st] = umma_desc(smem_u32(smem + L::kKV + st * L::kStage + 16384), 8192, 1024);
+      int stage = 0;
+#pragma unroll 1
+      for (int t = 0; t < ntiles; ++t) {
+        const int b = t & 1;
+        uint64_t vdesc = vd[0];
+#pragma unroll
+        for (int st = 1; st < STAGES; ++st) vdesc = stage == st ? vd[st] : vdesc;
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+          if (t >= g_tiles[gi]) continue;
+          // P of the tile is in shared memory; S of the tile (and so the K/V stage) was complete
+          // before the softmax could produce it
+          wait(p_full(gi, b), (t >> 1) & 1, 7000 + t);
+          if (t < 100 && gi == 0) tc_stamp(stamp_on, t * 8 + 5);
           tc_fence_after();
-          const uint32_t vst = smem_u32(smem + L::kKV + stage * L::kStage + 16384);
+          const uint32_t d = tmem + gi * kTcGroupCols + 128;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            umma_bf16(tmem + 128, umma_desc(p_base + j * 32, 16, 1024), umma_desc(vst + j * 2048, 8192, 1024),
-                      kIdescO, (t | j) ? 1u : 0u);
-          umma_commit(o_done);
-          umma_commit(&kv_empty[stage]);
+            umma_bf16(d, pd[gi][b] + ((j * 32) >> 4), vdesc + ((j * 2048) >> 4), kIdescO, (t | j) ? 1u : 0u);
+          umma_commit(o_done(gi, b));
+          if (t < 100 && gi == 0) tc_stamp(stamp_on, t * 8 + 6);
         }
+        umma_commit(&kv_empty[stage]);  // all PV of the tile issued; its S finished before P existed
+        if (++stage == STAGES) stage = 0;
       }
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTcCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kCols) : "memory");
   }
 }
 
