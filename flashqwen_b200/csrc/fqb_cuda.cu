@@ -467,7 +467,6 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   P.max_blocks = max_blocks;
   P.num_blocks = num_blocks;
   P.scale_log2 = scale * kLog2e;
-  P.dbg = std::getenv("FQB_PREFILL_DBG") ? std::atoi(std::getenv("FQB_PREFILL_DBG")) : 0;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
   if (use_tc) {
@@ -554,11 +553,6 @@ int fqb_device_status(int32_t* detail) {
   if (detail) std::memcpy(detail, h, sizeof(h));
   if (h[0] != 0)
     return set_error(h[0], "device status: code %d from kernel %d, block %d, value %d", h[0], h[1], h[2], h[3]);
-  return FQB_OK;
-}
-
-int fqb_debug_tc_timeline(long long* out, int n) {
-  FQB_CUDA_TRY(cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof(long long) * (n < 4096 ? n : 4096)));
   return FQB_OK;
 }
 

@@ -31,7 +31,6 @@ struct PrefillParams {
   const int* bt;
   int max_blocks, num_blocks;
   float scale_log2;
-  int dbg;  // tuning experiments only (0 in production)
 };
 
 // RT row tiles of 16 rows each -> BM = 16*RT query rows, 4*RT consumer warps + 1 producer warp

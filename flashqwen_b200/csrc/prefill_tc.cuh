@@ -29,9 +29,6 @@
 
 namespace fqb {
 
-__device__ long long g_tc_dbg[4096];
-__device__ __forceinline__ void tc_stamp(int on, int slot) { if (on && slot < 4096) g_tc_dbg[slot] = clock64(); }
-
 constexpr int kTcGroupRows = 32;  // query rows per group (x 4 q heads = one 128-row MMA tile)
 constexpr int kTcBN = 64;         // keys per tile
 constexpr int kTcGroupCols = 256; // TMEM columns per group: S0 [0,64), S1 [64,128), O [128,256)
@@ -200,7 +197,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
   }
   const int npages = cta_last < 0 ? 0 : cta_last / kTok + 1;
   const int ntiles = cta_last < 0 ? 0 : cta_last / kTcBN + 1;
-  const int stamp_on = (P.dbg & 256) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == gridDim.z - 1;
   bool dead = false;
   auto wait = [&](uint64_t* bar, uint32_t parity, int what) {
     if (!dead && !mbar_wait_bounded(bar, parity)) {
@@ -239,17 +235,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
     for (int k = 0; k < my_tiles; ++k) {
       const int b = k & 1;
       wait(s_full(gi, b), (k >> 1) & 1, k);
-      if (tid == 0 && k < 100) tc_stamp(stamp_on, k * 8 + 0);
       tc_fence_after();
       float x[kTcBN];
-      if (P.dbg & 8) {
 #pragma unroll
-        for (int j = 0; j < kTcBN; ++j) x[j] = static_cast<float>(j + k);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
-        tmem_wait_ld();
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
+      tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free(gi, b));
@@ -280,10 +270,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
       uint32_t pk[kTcBN / 2];
       const float neg_m = -m_used;
-      if (P.dbg & 1) {
-#pragma unroll
-        for (int j = 0; j < kTcBN / 2; ++j) pk[j] = __float_as_uint(x[j]);
-      } else
 #pragma unroll
       for (int j = 0; j < kTcBN; j += 4) {
         const float p0 = fast_exp2(fmaf(x[j], P.scale_log2, neg_m));
@@ -315,7 +301,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
         wait(o_done(gi, b), ((k - 2) >> 1) & 1, 1500 + k);
       }
       uint8_t* p_smem = p_group + b * 16384;
-      if (!(P.dbg & 2))
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *reinterpret_cast<uint4*>(p_smem + row * 128 + ((c ^ (row & 7)) << 4)) =
@@ -331,10 +316,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
           *reinterpret_cast<uint4*>(vst + (c >> 3) * 8192 + vr * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      if (!(P.dbg & 4)) proxy_fence_async();
+      proxy_fence_async();
       tc_fence_before();
       __syncwarp();
-      if (tid == 0 && k < 100) tc_stamp(stamp_on, k * 8 + 1);
       if (lane == 0) mbar_arrive(p_full(gi, b));
     }
     // ---- epilogue: O / l -> bf16 -> out ----
@@ -372,7 +356,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
     for (int k = 0; k < ntiles; ++k) {
       const int stage = k % STAGES;
       const int pg0 = k * 4;
-      const int npg = (P.dbg & 64) ? 1 : min(4, npages - pg0);
+      const int npg = min(4, npages - pg0);
       const int mine = lane < npg ? __ldg(btr + pg0 + lane) : 0;
       if (k >= STAGES) wait(&kv_empty[stage], ((k / STAGES) - 1) & 1, 3000 + k);
       if (lane < npg && static_cast<unsigned>(mine) >= static_cast<unsigned>(P.num_blocks))
@@ -409,9 +393,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
 #pragma unroll 1
       for (int k = 0; k < ntiles; ++k) {
         const int b = k & 1;
-        if (k < 100) tc_stamp(stamp_on, k * 8 + 2);
         wait(&kv_full[stage], kv_par, 5000 + k);
-        if (k < 100) tc_stamp(stamp_on, k * 8 + 3);
         uint64_t kdesc = kd[0];
 #pragma unroll
         for (int st = 1; st < STAGES; ++st) kdesc = stage == st ? kd[st] : kdesc;
@@ -431,7 +413,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
               umma_bf16(d, qd[gi] + ((kb * 16384 + j * 32) >> 4), kdesc + ((kb * 8192 + j * 32) >> 4), kIdescS,
                         (kb | j) ? 1u : 0u);
           umma_commit(s_full(gi, b));
-          if (k < 100 && gi == 0) tc_stamp(stamp_on, k * 8 + 4);
         }
         if (++stage == STAGES) {
           stage = 0;
@@ -465,14 +446,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
           // P of the tile is in shared memory; S of the tile (and so the K/V stage) was complete
           // before the softmax could produce it
           wait(p_full(gi, b), (t >> 1) & 1, 7000 + t);
-          if (t < 100 && gi == 0) tc_stamp(stamp_on, t * 8 + 5);
           tc_fence_after();
           const uint32_t d = tmem + gi * kTcGroupCols + 128;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             umma_bf16(d, pd[gi][b] + ((j * 32) >> 4), vdesc + ((j * 2048) >> 4), kIdescO, (t | j) ? 1u : 0u);
           umma_commit(o_done(gi, b));
-          if (t < 100 && gi == 0) tc_stamp(stamp_on, t * 8 + 6);
         }
         umma_commit(&kv_empty[stage]);  // all PV of the tile issued; its S finished before P existed
         if (++stage == STAGES) stage = 0;
