@@ -137,9 +137,9 @@ using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
-// independent launches with 2 or 1 local heads: three small CTAs (of three different launches) per SM
+// a smaller two-head shape (three CTAs of three different launches per SM); measured slower than
+// DecodeCfg2 for independent launches, kept for comparison
 using DecodeCfg2i = DecodeCfg<2, 4, 2, 3, 256>;
-using DecodeCfg1i = DecodeCfg<2, 4, 1, 3, 256>;
 
 unsigned next_epoch() {
   static std::atomic<unsigned> counter{0x5eed0000u};
@@ -350,8 +350,13 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
         P.kvh_base = base;
         int rc, took;
         if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) { rc = launch_decode<DecodeCfg2i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
-        else { rc = launch_decode<DecodeCfg1i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        else if (left >= 2) {
+          static const bool small2 = std::getenv("FQB_DECODE_H2_SMALL") != nullptr;  // tuning aid
+          rc = small2 ? launch_decode<DecodeCfg2i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st)
+                      : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st);
+          took = 2;
+        }
+        else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
         P.sync_first = 0;  // later launches of the call serve other heads: disjoint partials and counters
