@@ -208,9 +208,22 @@ def fqb_runner(w):
     launches = {"n": 0}
     fq.device_status_reset()
 
+    plan = torch.empty(4 * w.batch + 4, dtype=torch.int32, device=w.dev)
+    use_plan = w.batch <= 256
+
+    def make_plan(pos, qstart, rids):
+        """Once per step: the decode metadata resolved for all layers (fqb_attn_decode_plan)."""
+        if use_plan:
+            fq.attn_decode_plan(pos, qstart, rids, w.batch, w.max_blocks, plan)
+            launches["n"] += 1
+
     def decode(layer, qkv, bt, pos, qstart, rids, stream=None, flags=0):
-        fq.attn_decode(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
-                       qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
+        if use_plan:
+            fq.attn_decode_planned(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD,
+                                   plan, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
+        else:
+            fq.attn_decode(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
+                           qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
         if flags and w.batch <= 256:
             launches["n"] += 2 if w.kvl == 8 else 1  # 8 heads go as two launches of 4
         else:
@@ -225,7 +238,7 @@ def fqb_runner(w):
     def check():
         fq.device_status()
 
-    return decode, append, launches, check
+    return decode, append, launches, check, make_plan
 
 
 def ref_runner(w):
@@ -253,7 +266,7 @@ def ref_runner(w):
                          w.max_blocks, req.data_ptr(), pos.data_ptr(), w.batch, st(stream))
         launches["n"] += 1
 
-    return decode, append, launches, lambda: None
+    return decode, append, launches, lambda: None, lambda pos, qstart, rids: None
 
 
 def time_region(fn, steps, warmup, dist_on, dev):
@@ -513,11 +526,12 @@ def main():
         print(json.dumps(line))
         return
 
-    decode, append, launches, check = (ref_runner if reference else fqb_runner)(w)
+    decode, append, launches, check, make_plan = (ref_runner if reference else fqb_runner)(w)
 
     # ---- kernel-only: everything resident ----
     def measure_resident(flags, use_graph):
         def step_resident():
+            make_plan(w.pos, w.qstart, w.rids)
             for layer in range(a.layers):
                 if flags:
                     decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=flags)
@@ -566,6 +580,7 @@ def main():
         gathered = torch.empty((world, a.batch, w.hl * HD), dtype=torch.bfloat16, device=dev)
 
         def step_gather():
+            make_plan(w.pos, w.qstart, w.rids)
             for layer in range(a.layers):
                 decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
                 torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
@@ -605,6 +620,8 @@ def main():
                     ev_in[i].record(copy_in)
             for i, (l0, l1) in enumerate(chunks):
                 main.wait_event(ev_in[i])
+                if i == 0:
+                    make_plan(d_pos, d_qstart, d_rids)
                 for layer in range(l0, l1):
                     append(layer, d_qkv, d_bt, d_req, d_pos)
                     decode(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids)

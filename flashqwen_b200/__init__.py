@@ -12,6 +12,8 @@ from .ops import (  # noqa: F401
     DECODE_INDEPENDENT,
     KvStore,
     attn_decode,
+    attn_decode_plan,
+    attn_decode_planned,
     attn_decode_static,
     attn_prefill,
     copy_blocks,

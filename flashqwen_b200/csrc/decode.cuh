@@ -49,6 +49,7 @@ struct DecodeParams {
   int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
   int independent; // 1: nothing this launch reads is written by the kernel launched before it
   int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
+  const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
 };
 
 // Scratch layout. Partial (sequence di, CTA b, kv head, q head g) lives at slot
@@ -149,6 +150,50 @@ __device__ __forceinline__ void merge_pair(const DecodeParams& P, int di, int kv
   }
 }
 
+// Step plan: what every decode launch of a step derives from pos / qstart / decode_rids, computed
+// once. plan[4*di .. 4*di+3] = {request r, flat row, last key position (clamped, -1 = no key), first
+// page index in the flat page list}; plan[4*n] = total pages. One CTA, up to 1024 sequences.
+__global__ void __launch_bounds__(1024)
+decode_plan_kernel(const int* __restrict__ pos, const int* __restrict__ qstart, const int* __restrict__ rids,
+                   int n_decode, int max_blocks, int* __restrict__ plan) {
+  __shared__ int s_pages[1024];
+  __shared__ int s_warp[32];
+  const int di = threadIdx.x, lane = di & 31, warp = di >> 5;
+  int r = 0, flat = 0, qp = -1;
+  if (di < n_decode) {
+    r = rids[di];
+    flat = qstart[r];
+    qp = pos[flat];
+    if (qp >= max_blocks * kTok) {
+      report(FQB_ERR_INDEX, kKidDecode, qp);
+      qp = max_blocks * kTok - 1;
+    }
+    if (qp < 0) qp = -1;
+  }
+  const int pages = di < n_decode ? (qp + kTok) / kTok : 0;
+  int incl = pages;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  s_pages[di] = incl - pages;
+  __syncthreads();
+  if (warp == 0) {
+    int w = s_warp[lane];
+    int wi = w;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += y;
+    }
+    s_warp[lane] = wi - w;
+    if (lane == 31) plan[4 * n_decode] = wi;
+  }
+  __syncthreads();
+  if (di < n_decode)
+    reinterpret_cast<int4*>(plan)[di] = make_int4(r, flat, qp, s_pages[di] + s_warp[warp]);
+}
+
 // HEADS = local kv heads (1, 2, 4 or 8); SUB = NW / HEADS warps share one head's pages.
 template <int NW, int NS, int HEADS, int MINB, int MAXD>
 __global__ void __launch_bounds__(NW * 32, MINB)
@@ -180,7 +225,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     for (int i = 0; i < NW * NS; ++i) mbar_init(&bars[i], 1);
     mbar_fence_init();
   }
-  // ---- per-sequence metadata (3 dependent loads) and the page prefix sum ----
+  // ---- per-sequence metadata and the page prefix sum ----
+  // With a step plan (built once per step, the same for all layers) this is one coalesced load;
+  // without it, three dependent loads per sequence and a scan.
+  const bool planned = P.plan != nullptr;
+  if (planned) {
+    for (int di = tid; di < n_decode; di += NW * 32) {
+      const int4 e = __ldg(reinterpret_cast<const int4*>(P.plan) + di);
+      s_r[di] = e.x;
+      s_flat[di] = e.y;
+      s_qpos[di] = e.z;
+      s_cum[di] = e.w;
+    }
+    if (tid == 0) s_cum[n_decode] = __ldg(P.plan + 4 * n_decode);
+  } else
   for (int di = tid; di < n_decode; di += NW * 32) {
     const int r = P.rids[di];
     const int flat = P.qstart[r];
@@ -208,7 +266,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
         uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(s_flat[di]) * P.n_heads * kHd);
         for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
       }
-  if (warp == 0) {
+  if (warp == 0 && !planned) {
     constexpr int kPer = MAXD / 32;
     int sum = 0;
     for (int i = 0; i < kPer; ++i) {

@@ -286,12 +286,27 @@ int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max
   return regions * one;
 }
 
-int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids, int n_decode,
+                         int max_blocks, int32_t* plan, void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (!pos || !qstart || !decode_rids || !plan) return set_error(FQB_ERR_INVALID, "attn_decode_plan: null pointer");
+  if (n_decode > FQB_PLAN_MAX_DECODE)
+    return set_error(FQB_ERR_SHAPE, "attn_decode_plan: %d sequences, at most %d", n_decode, FQB_PLAN_MAX_DECODE);
+  if (reinterpret_cast<uintptr_t>(plan) & 15u) return set_error(FQB_ERR_INVALID, "attn_decode_plan: plan must be 16-byte aligned");
+  decode_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(pos, qstart, decode_rids, n_decode, max_blocks,
+                                                                        plan);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
+static int decode_impl(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
                        int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
-                       void* stream) {
+                       const int32_t* plan, void* stream) {
   if (n_decode <= 0) return FQB_OK;
+  if (plan && (n_decode > 256 || (reinterpret_cast<uintptr_t>(plan) & 15u)))
+    return set_error(FQB_ERR_INVALID, "attn_decode: a step plan serves at most 256 sequences per call and must be 16-byte aligned");
   if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
   if (!q || !cache || !out || !pos || !qstart || !decode_rids || !bt || !pm || !pl || !pa)
     return set_error(FQB_ERR_INVALID, "attn_decode: null pointer");
@@ -324,6 +339,7 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
   P.partial_slots = partial_slots;
   P.independent = 0;
   P.sync_first = 0;
+  P.plan = plan;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // ---- independent launches: one CTA per SM per launch, two launches resident side by side ----
@@ -379,6 +395,25 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
     base += took;
   }
   return FQB_OK;
+}
+
+int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                       int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                       const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
+                       float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
+                       void* stream) {
+  return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
+                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, stream);
+}
+
+int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                            int n_kv, int head_dim, const int32_t* plan, int n_decode, const int32_t* bt,
+                            int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
+                            int64_t partial_slots, unsigned flags, void* stream) {
+  if (n_decode > 0 && !plan) return set_error(FQB_ERR_INVALID, "attn_decode_planned: null plan");
+  // pos / qstart / decode_rids are not read when a plan is given; the plan pointer stands in for them
+  return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, plan, plan, plan, n_decode, bt,
+                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, stream);
 }
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,

@@ -117,7 +117,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
   using L = TcSmem<G, STAGES>;
   static_assert(G >= 1 && G <= 2 && STAGES >= 2 && STAGES <= 4, "barrier block and TMEM are laid out for these");
   constexpr int kCols = G * kTcGroupCols;
-  constexpr int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1, kPvWarp = 4 * G + 2;
+  constexpr int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;  // warp 4G+2 issues PV
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base

@@ -68,6 +68,20 @@ def attn_decode(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim,
                                  _stream(stream)), "fqb_attn_decode")
 
 
+def attn_decode_plan(pos, qstart, decode_rids, n_decode, max_blocks, plan, stream=None):
+    """fqb_attn_decode_plan: the step's decode metadata resolved once for all layers (plan: int32[4*n+1])."""
+    check(lib.fqb_attn_decode_plan(_ptr(pos), _ptr(qstart), _ptr(decode_rids), n_decode, max_blocks, _ptr(plan),
+                                   _stream(stream)), "fqb_attn_decode_plan")
+
+
+def attn_decode_planned(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, plan, n_decode, bt,
+                        max_blocks, block_size, scale, pm, pl, pa, partial_slots, stream=None, flags=0):
+    """fqb_attn_decode_planned: fqb_attn_decode_ex with the step plan in place of pos / qstart / decode_rids."""
+    check(lib.fqb_attn_decode_planned(_ptr(q), q_stride, _ptr(cache_kv), num_blocks, _ptr(out), n_heads, n_kv, head_dim,
+                                      _ptr(plan), n_decode, _ptr(bt), max_blocks, block_size, scale, _ptr(pm), _ptr(pl),
+                                      _ptr(pa), partial_slots, flags, _stream(stream)), "fqb_attn_decode_planned")
+
+
 def attn_decode_static(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                        n_decode, bt, max_blocks, block_size, scale, stream=None):
     """fqb_attn_decode_static: decode attention with the library's built-in scratch, for callers that

@@ -127,6 +127,22 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
                        const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
                        float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
 
+/* Step plan. The per-sequence values every decode launch derives from pos / qstart / decode_rids
+ * (request, flat row, last key position, page prefix sum) are the same for all layers of a step:
+ * fqb_attn_decode_plan computes them once (one small kernel) into plan[4*n_decode + 1] int32 (device,
+ * 16-byte aligned), and fqb_attn_decode_planned takes the plan instead of the three arrays, which
+ * turns each launch's three dependent metadata loads and its scan into one coalesced load. No
+ * reference counterpart (the reference recomputes per launch, engine/src/attn_cute.cu:172). The plan
+ * is valid while pos / qstart / decode_rids are unchanged; at most FQB_PLAN_MAX_DECODE sequences to
+ * build and 256 per planned call. Results are identical to fqb_attn_decode_ex. */
+#define FQB_PLAN_MAX_DECODE 1024
+int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
+                         int n_decode, int max_blocks, int32_t* plan, void* stream);
+int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
+                            int n_heads, int n_kv, int head_dim, const int32_t* plan, int n_decode,
+                            const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                            float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
+
 /* Decode attention without caller scratch. No counterpart in the reference (its call site always
  * passes pm / pl / pa): this entry point exists for callers that have no device memory to give and
  * no way to get any at the point of the call -- an engine that handed all free VRAM to its KV pool

@@ -212,3 +212,45 @@ def test_decode_inside_a_cuda_graph_with_changing_lengths():
     torch.cuda.synchronize()
     fq.device_status()
     assert maxabs(host(out), oracle_decode(c2)) <= TOL
+
+
+@pytest.mark.parametrize("flags", [0, 1])
+@pytest.mark.parametrize("n_kv", [8, 1])
+def test_step_plan_gives_identical_results(flags, n_kv):
+    """The plan only replaces how a launch finds its per-sequence metadata: outputs are bit-identical."""
+    lengths = [700, 33, 1500, 16, 250, 4000, 1, 17]
+    c = synth.decode_case(lengths, 520, seed=400 + n_kv, n_kv=n_kv, shuffle_rids=True)
+    c.pos[3] = -1  # a sequence without keys goes through the plan too
+    cache, qkv = dv(c.cache), dv(c.qkv)
+    pos, qstart, rids, bt = dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt)
+    n = len(lengths)
+    plan = torch.full((4 * n + 1 + 3,), -77, dtype=torch.int32, device=DEV)
+    fq.attn_decode_plan(pos, qstart, rids, n, c.max_blocks, plan)
+    torch.cuda.synchronize()
+    hp = plan.cpu().numpy()
+    qp = np.where(c.pos[c.qstart[c.decode_rids]] < 0, -1, c.pos[c.qstart[c.decode_rids]])
+    pages = (qp + 16) // 16
+    want = np.stack([c.decode_rids, c.qstart[c.decode_rids], qp, np.concatenate([[0], np.cumsum(pages)[:-1]])], 1)
+    assert np.array_equal(hp[:4 * n].reshape(n, 4), want) and hp[4 * n] == pages.sum() and (hp[4 * n + 1:] == -77).all()
+    s = Scratch(n, n_kv * 4, c.max_blocks)
+    outs = []
+    for planned in (False, True):
+        out = torch.full((n, n_kv * 4 * 128), 0x7FC0, dtype=torch.int16, device=DEV)
+        for _ in range(3):
+            if planned:
+                fq.attn_decode_planned(qkv, c.q_stride, cache, c.num_blocks, out, n_kv * 4, n_kv, 128, plan, n, bt,
+                                       c.max_blocks, 16, c.scale, s.pm, s.pl, s.pa, s.slots, flags=flags)
+            else:
+                fq.attn_decode(qkv, c.q_stride, cache, c.num_blocks, out, n_kv * 4, n_kv, 128, pos, qstart, rids, n, bt,
+                               c.max_blocks, 16, c.scale, s.pm, s.pl, s.pa, s.slots, flags=flags)
+        torch.cuda.synchronize()
+        fq.device_status()
+        outs.append(host(out))
+    assert np.array_equal(outs[0], outs[1])
+    assert maxabs(outs[1], oracle_decode(c)) <= TOL
+
+
+@pytest.mark.parametrize("n_kv", [3, 16])
+def test_head_counts_that_need_several_launches(n_kv):
+    c = synth.decode_case([300, 48, 1025, 7], 128, seed=500 + n_kv, n_kv=n_kv)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
