@@ -62,6 +62,7 @@ def parse():
                     help="issue the resident step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--dependent", dest="independent", action="store_false",
                     help="resident loop without FQB_DECODE_INDEPENDENT: every launch waits for the one before it")
+    ap.add_argument("--skip-dependent", action="store_true", help="do not also time the dependent-launch variant")
     ap.add_argument("--workload", default="decode", choices=["decode", "cfg3", "copy"],
                     help="decode: the headline step. cfg3: KV append + chunked prefill (4 x 512-row chunks over "
                          "histories 0/1024/3000/7000). copy: prefix-block copy-on-write copies over 36 layers")
@@ -568,7 +569,7 @@ def main():
     layer_s = ms_step * 1e-3 / a.layers
     achieved = w.bytes_layer_rank / layer_s / 1e9
     dependent = None
-    if dflags:  # the same step with every launch waiting for the one before it
+    if dflags and not a.skip_dependent:  # the same step with every launch waiting for the one before it
         ms_d, _ = measure_resident(0, a.graph)
         check()
         dependent = {"ms_per_step": round(ms_d / a.steps, 4),

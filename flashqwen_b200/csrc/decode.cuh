@@ -296,7 +296,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   const int W = max(2 * SUB, (total_pages + nb - 1) / nb);  // pages per CTA
   const long long lo_ll = static_cast<long long>(blockIdx.x) * W;
   if (lo_ll >= total_pages) {  // whole CTA leaves together; nothing in flight
-    pdl_wait();
+    if (blockIdx.x == 0) pdl_wait();
     return;
   }
   const int lo = static_cast<int>(lo_ll);
@@ -314,15 +314,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   int p_page = pc.pb + sub;
   int p_blk = 0;
   int islot = 0;
-  auto prod_settle = [&]() {  // move to the next item until this warp has a page in it
+  // Moves to the next item until this warp has a page in it; with `load` it also fetches that
+  // page's block id (used one page later, so the fetch is off the critical path in steady state).
+  auto prod_settle = [&](bool load) {
     while (pc.off < hi && p_page >= pc.pe) {
       item_at(pc, pc.off + (pc.pe - pc.pb), hi, n_decode, s_cum);
       p_page = pc.pb + sub;
     }
-    if (pc.off < hi)
+    if (load && pc.off < hi)
       p_blk = __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page);
   };
-  auto prod_issue = [&]() {
+  auto prod_issue = [&](bool load_next) {
     if (pc.off >= hi) return;
     if (static_cast<unsigned>(p_blk) >= static_cast<unsigned>(P.num_blocks))
       report(FQB_ERR_INDEX, kKidDecode, p_blk);  // the load below then reads zeros
@@ -332,11 +334,26 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     }
     islot = (islot + 1 == NS) ? 0 : islot + 1;
     p_page += SUB;
-    prod_settle();
+    prod_settle(load_next);
   };
-  prod_settle();
-#pragma unroll 1
-  for (int s = 0; s < NS; ++s) prod_issue();
+  // Filling the ring: the block ids of this warp's first NS pages are fetched with ONE load (lane j
+  // takes the j-th page) instead of NS dependent ones.
+  prod_settle(false);
+  {
+    const int n_first = pc.off < hi ? min(NS, (pc.pe - p_page + SUB - 1) / SUB) : 0;
+    const int pre = lane < n_first
+                        ? __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page + lane * SUB)
+                        : 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (s < n_first) {
+        p_blk = __shfl_sync(0xffffffffu, pre, s);
+        prod_issue(s + 1 >= n_first);  // the last prefetched page goes back to the one-ahead scheme
+      } else {
+        prod_issue(true);
+      }
+    }
+  }
 
   // ---- consumer ----
   const int g = lane >> 2, t = lane & 3;
@@ -433,7 +450,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       __syncwarp();  // every lane has read the buffer before it is refilled
       cslot = (cslot + 1 == NS) ? 0 : cslot + 1;
       if (cslot == 0) cphase ^= 1u;
-      prod_issue();
+      prod_issue(true);
     }
 
     // ---- end of item: this warp's softmax state of (cc.di, kvh) over its pages ----
@@ -545,7 +562,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       qa[ks][1] = qn[ks][1];
     }
   }
-  pdl_wait();  // a kernel never completes before the one launched ahead of it
+  // A kernel never completes before the one launched ahead of it: CTA 0 stays until that one is
+  // done. Only CTA 0 -- a CTA that waits keeps its shared memory, and with every CTA waiting a
+  // quarter of each CTA's residency was spent idle here instead of hosting the next launch.
+  if (blockIdx.x == 0) pdl_wait();
 }
 
 }  // namespace fqb
