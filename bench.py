@@ -314,7 +314,7 @@ def cpu_oracle_rate(w, a, budget_s=20.0):
     cache = pool.view(torch.int16).numpy().view(np.uint16)
     rids = np.arange(w.batch, dtype=np.int32)
     spent, done = 0.0, 0
-    while spent < budget_s and done < 4 * w.layers:
+    while spent < budget_s and done < 12 * w.layers:
         qkv = w.h_qkv[done % w.layers].view(torch.int16).numpy().view(np.uint16)
         t0 = time.perf_counter()
         O.attn_decode(qkv, QKV_DIM, cache, N_HEADS, N_KV, pos, qstart, rids, bt, w.scale, rows=w.batch, nthreads=cores)

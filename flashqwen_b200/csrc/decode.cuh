@@ -289,7 +289,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     const int total = __shfl_sync(0xffffffffu, incl, 31);
     if (lane == 0) s_cum[n_decode] = total;
   }
-  __syncthreads();
+  if (!planned) __syncthreads();  // the scan's results; a plan was complete at the barrier above
 
   const int total_pages = s_cum[n_decode];
   const int nb = static_cast<int>(gridDim.x);
