@@ -138,13 +138,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
   auto q_full = [&](int gi) { return bars + 8 + 10 * gi + 8; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
-  const int r = P.rids[blockIdx.z];
+  // Longest jobs first: CTAs are handed out in blockIdx order (x fastest, z slowest), a job's length
+  // is its last visible key position, and one CTA per SM runs at a time, so the z-th CTA plane takes
+  // the request with the z-th longest key range (ranked here on the device; up to 32 requests, more
+  // keep their given order) and x walks its query tiles from the last one down.
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int zsel = blockIdx.z;
+  if (gridDim.z > 1 && gridDim.z <= 32) {
+    int len = -1;
+    if (lane < static_cast<int>(gridDim.z)) {
+      const int rr = P.rids[lane];
+      const int n = P.qlen[rr];
+      len = n > 0 ? P.pos[P.qstart[rr] + n - 1] : -1;
+    }
+    int rank = 0;
+    for (int j = 0; j < static_cast<int>(gridDim.z); ++j) {
+      const int other = __shfl_sync(0xffffffffu, len, j);
+      rank += (other > len || (other == len && j < lane)) ? 1 : 0;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, lane < static_cast<int>(gridDim.z) && rank == static_cast<int>(blockIdx.z));
+    zsel = hit ? __ffs(hit) - 1 : static_cast<int>(blockIdx.z);
+  }
+  const int r = P.rids[zsel];
   const int kvh = blockIdx.y;
   const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
   const int ql = P.qlen[r], qs = P.qstart[r];
   const int q0 = qtile * L::kRows;
   if (q0 >= ql) return;  // before any allocation; the whole CTA leaves together
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
