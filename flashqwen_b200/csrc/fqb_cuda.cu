@@ -522,10 +522,17 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
       FQB_CUDA_TRY(cudaGetLastError());
       return FQB_OK;
     };
-    if (variant == 13) return go(prefill_tc_kernel<1, 3>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32);
-    if (variant == 14) return go(prefill_tc_kernel<1, 4>, TcSmem<1, 4>::kAlloc, TcSmem<1, 4>::kThreads, 32);
-    if (variant == 22) return go(prefill_tc_kernel<2, 2>, TcSmem<2, 2>::kAlloc, TcSmem<2, 2>::kThreads, 64);
-    return go(prefill_tc_kernel<2, 3>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
+    // FQB_PREFILL_SMEM_P=1 routes P through shared memory instead of tensor memory (comparison)
+    static const bool smem_p = std::getenv("FQB_PREFILL_SMEM_P") != nullptr;
+    if (smem_p) {
+      if (variant == 13) return go(prefill_tc_kernel<1, 3, false>, TcSmem<1, 3, false>::kAlloc, TcSmem<1, 3, false>::kThreads, 32);
+      return go(prefill_tc_kernel<2, 3, false>, TcSmem<2, 3, false>::kAlloc, TcSmem<2, 3, false>::kThreads, 64);
+    }
+    if (variant == 13) return go(prefill_tc_kernel<1, 3, true>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32);
+    if (variant == 15) return go(prefill_tc_kernel<1, 5, true>, TcSmem<1, 5>::kAlloc, TcSmem<1, 5>::kThreads, 32);
+    if (variant == 24) return go(prefill_tc_kernel<2, 4, true>, TcSmem<2, 4>::kAlloc, TcSmem<2, 4>::kThreads, 64);
+    if (variant == 25) return go(prefill_tc_kernel<2, 5, true>, TcSmem<2, 5>::kAlloc, TcSmem<2, 5>::kThreads, 64);
+    return go(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
   }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;

@@ -36,13 +36,13 @@ constexpr int kTcGroupCols = 256; // TMEM columns per group: S0 [0,64), S1 [64,1
 // G = row groups per CTA (1 or 2): each group is a 128-row MMA tile with its own Q, P, S and O; the
 // groups share the K/V stages, so with G = 2 every K/V tile fetched from L2 feeds twice the math and
 // the softmax of one group overlaps the MMAs of the other.
-template <int G, int STAGES>
+template <int G, int STAGES, bool TS = true>
 struct TcSmem {
   static constexpr int kQ = 0;                                   // G x [2 k-blocks][128 rows][128 B]
   static constexpr int kKV = G * 32768;                          // stages x {K 16 KiB, V 16 KiB}
   static constexpr int kStage = 32768;
   static constexpr int kP = kKV + STAGES * kStage;               // G x 2 x [128 rows][128 B]
-  static constexpr int kBars = kP + G * 2 * 16384;
+  static constexpr int kBars = kP + (TS ? 0 : G * 2 * 16384);      // no P tiles when P lives in TMEM
   static constexpr int kTmemSlot = kBars + 32 * 8;
   static constexpr int kTotal = kTmemSlot + 16;
   static constexpr int kAlloc = kTotal;                          // base must be 1024-byte aligned (checked)
@@ -71,6 +71,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t 
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// the same MMA with the A operand read from tensor memory (128 lanes x 8 columns of bf16 pairs)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -111,11 +119,14 @@ __device__ __forceinline__ void tma_load_half(void* dst, const CUtensorMap* m, u
   tma_load_page(dst, m, bar, 0, 0, half, plane, blk);
 }
 
-template <int G, int STAGES>
-__global__ void __launch_bounds__(TcSmem<G, STAGES>::kThreads, 1)
+// TS: P stays in tensor memory (it overwrites the first 32 columns of the S tile it came from, as
+// packed bf16 pairs) and is the A operand of the PV MMA from there, instead of going through a
+// swizzled shared-memory tile.
+template <int G, int STAGES, bool TS>
+__global__ void __launch_bounds__(TcSmem<G, STAGES, TS>::kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) {
-  using L = TcSmem<G, STAGES>;
-  static_assert(G >= 1 && G <= 2 && STAGES >= 2 && STAGES <= 4, "barrier block and TMEM are laid out for these");
+  using L = TcSmem<G, STAGES, TS>;
+  static_assert(G >= 1 && G <= 2 && STAGES >= 2 && STAGES <= 5, "barrier block and TMEM are laid out for these");
   constexpr int kCols = G * kTcGroupCols;
   constexpr int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;  // warp 4G+2 issues PV
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -125,17 +136,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-  uint64_t* kv_full = bars;        // [4]  producer -> MMA (tx bytes)
-  uint64_t* kv_empty = bars + 4;   // [4]  MMA commit -> producer
-  // per group gi at bars + 8 + 10*gi: s_full[2] (MMA commit -> softmax), s_free[2] (softmax, 1 per warp ->
+  uint64_t* kv_full = bars;        // [5]  producer -> MMA (tx bytes)
+  uint64_t* kv_empty = bars + 5;   // [5]  MMA commit -> producer
+  // per group gi at bars + 10 + 10*gi: s_full[2] (MMA commit -> softmax), s_free[2] (softmax, 1 per warp ->
   // MMA), p_full[2] (softmax, 1 per warp -> MMA), o_done[2] (MMA commit -> softmax), q_full. S, P and
   // their barriers are double-buffered by tile parity, so the softmax of tile k+1 never waits for the
   // MMA round trip of tile k (a single P buffer tied every tile to two cross-warp hand-offs).
-  auto s_full = [&](int gi, int b) { return bars + 8 + 10 * gi + b; };
-  auto s_free = [&](int gi, int b) { return bars + 8 + 10 * gi + 2 + b; };
-  auto p_full = [&](int gi, int b) { return bars + 8 + 10 * gi + 4 + b; };
-  auto o_done = [&](int gi, int b) { return bars + 8 + 10 * gi + 6 + b; };
-  auto q_full = [&](int gi) { return bars + 8 + 10 * gi + 8; };
+  auto s_full = [&](int gi, int b) { return bars + 10 + 10 * gi + b; };
+  auto s_free = [&](int gi, int b) { return bars + 10 + 10 * gi + 2 + b; };
+  auto p_full = [&](int gi, int b) { return bars + 10 + 10 * gi + 4 + b; };
+  auto o_done = [&](int gi, int b) { return bars + 10 + 10 * gi + 6 + b; };
+  auto q_full = [&](int gi) { return bars + 10 + 10 * gi + 8; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
   // Longest jobs first: CTAs are handed out in blockIdx order (x fastest, z slowest), a job's length
@@ -262,7 +273,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(s_free(gi, b));
+      if (!TS && lane == 0) mbar_arrive(s_free(gi, b));  // with TS the S tile is free only after PV has read P from it
       const int k0 = k * kTcBN;
       if (k0 + kTcBN - 1 > qp) {  // the tile crosses this row's causal edge (or lies beyond it)
 #pragma unroll
@@ -320,11 +331,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
       } else if (k >= 2) {
         wait(o_done(gi, b), ((k - 2) >> 1) & 1, 1500 + k);
       }
-      uint8_t* p_smem = p_group + b * 16384;
+      if (TS) {
+        // P over the first 32 columns of S[b]: column c = keys 2c (low half) and 2c+1 (high half)
+        float pf[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(p_smem + row * 128 + ((c ^ (row & 7)) << 4)) =
-            make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+        for (int c = 0; c < 32; ++c) pf[c] = __uint_as_float(pk[c]);
+        tmem_st16(lane_addr + b * 64, pf);
+        tmem_st16(lane_addr + b * 64 + 16, pf + 16);
+        tmem_wait_st();
+      } else {
+        uint8_t* p_smem = p_group + b * 16384;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(p_smem + row * 128 + ((c ^ (row & 7)) << 4)) =
+              make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+      }
       if (k == ntiles - 1) {
         // key slots past the CTA's last position (never written, or pages that do not exist): clear
         // their V rows so that 0 * garbage cannot reach an accumulator. Keys between this group's
@@ -423,7 +444,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
 #pragma unroll
         for (int gi = 0; gi < G; ++gi) {
           if (k >= g_tiles[gi]) continue;  // this group's rows cannot see the tile
-          if (k >= 2) wait(s_free(gi, b), ((k >> 1) - 1) & 1, 6000 + k);
+          if (k >= 2) {
+            if (TS) wait(o_done(gi, b), ((k - 2) >> 1) & 1, 6000 + k);  // PV of tile k-2 has read P out of this tile
+            else wait(s_free(gi, b), ((k >> 1) - 1) & 1, 6000 + k);
+          }
           tc_fence_after();
           const uint32_t d = tmem + gi * kTcGroupCols + b * 64;
 #pragma unroll
@@ -469,8 +493,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams 
           tc_fence_after();
           const uint32_t d = tmem + gi * kTcGroupCols + 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            umma_bf16(d, pd[gi][b] + ((j * 32) >> 4), vdesc + ((j * 2048) >> 4), kIdescO, (t | j) ? 1u : 0u);
+          for (int j = 0; j < 4; ++j) {
+            if (TS)
+              umma_bf16_ts(d, tmem + gi * kTcGroupCols + b * 64 + j * 8, vdesc + ((j * 2048) >> 4), kIdescO,
+                           (t | j) ? 1u : 0u);
+            else
+              umma_bf16(d, pd[gi][b] + ((j * 32) >> 4), vdesc + ((j * 2048) >> 4), kIdescO, (t | j) ? 1u : 0u);
+          }
           umma_commit(o_done(gi, b));
         }
         umma_commit(&kv_empty[stage]);  // all PV of the tile issued; its S finished before P existed
