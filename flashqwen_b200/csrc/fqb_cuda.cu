@@ -15,6 +15,7 @@
 #include "kv_append.cuh"
 #include "prefill.cuh"
 #include "prefill_tc.cuh"
+#include "prefill_tc_ks.cuh"
 
 namespace fqb {
 namespace {
@@ -512,9 +513,11 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   if (use_tc) {
     if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
       return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
-    // FQB_PREFILL_TC=<groups><stages> picks row groups per CTA and K/V stages (tuning aid); default 23
+    // Default: the key-split kernel (32 query rows per CTA, the two halves of the key range run as two
+    // concurrent pipelines). FQB_PREFILL_TC=<groups><stages> selects the row-group kernel instead
+    // (23 = two row groups sharing 3 K/V stages, 13 / 15 = one group); both are kept for comparison.
     const char* v = std::getenv("FQB_PREFILL_TC");
-    const int variant = v ? std::atoi(v) : 23;
+    const int variant = v ? std::atoi(v) : 93;
     auto go = [&](auto kern, int smem, int threads, int rows) -> int {
       FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       dim3 grid((max_qlen + rows - 1) / rows, n_kv, R);
@@ -532,7 +535,8 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
     if (variant == 15) return go(prefill_tc_kernel<1, 5, true>, TcSmem<1, 5>::kAlloc, TcSmem<1, 5>::kThreads, 32);
     if (variant == 24) return go(prefill_tc_kernel<2, 4, true>, TcSmem<2, 4>::kAlloc, TcSmem<2, 4>::kThreads, 64);
     if (variant == 25) return go(prefill_tc_kernel<2, 5, true>, TcSmem<2, 5>::kAlloc, TcSmem<2, 5>::kThreads, 64);
-    return go(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
+    if (variant == 23) return go(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
+    return go(prefill_tc_ks_kernel<3>, TcKsSmem<3>::kAlloc, TcKsSmem<3>::kThreads, 32);
   }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;
