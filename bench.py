@@ -674,8 +674,12 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
             "tokens_per_s_per_layer": round(a.batch / layer_s, 1),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(w.key) if world == 1 else None,
-                         "peak_source": peak_src, "kernel": "decode_kernel (split-K + fused combine), one launch per layer, per GPU",
+                         "frac": round(achieved / peak, 4),
+                         "traffic": NCU_TRAFFIC_BYTES.get(w.key) if (world == 1 and not reference and not a.shard_of) else None,
+                         "peak_source": peak_src,
+                         "kernel": ("CuteDecodeSplitKernel + CuteDecodeCombineKernel (reference), two launches per layer"
+                                    if reference else
+                                    "decode_kernel (split-K + fused combine), per layer, per GPU"),
                          "algorithmic_bytes_per_launch": w.bytes_layer_rank,
                          "launch_us": round(layer_s * 1e6, 3)},
             "clocks": clocks, "gpu_launches": n_launch}

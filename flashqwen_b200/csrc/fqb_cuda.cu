@@ -171,6 +171,34 @@ cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
+// One launcher for the tcgen05 prefill kernels: opts the kernel in to its dynamic shared memory once
+// per device and thread, then launches (query tiles, kv heads, requests).
+template <class Kern>
+int launch_prefill_tc(Kern kern, int smem, int threads, int rows, int max_qlen, int n_kv, int R, const CUtensorMap& map,
+                      const PrefillParams& P, cudaStream_t st) {
+  // the kernels share one function-pointer type, so the "already opted in" memo is keyed by pointer
+  struct Memo {
+    const void* fn;
+    int dev;
+  };
+  static thread_local Memo memo[8] = {};
+  int dev = 0;
+  FQB_CUDA_TRY(cudaGetDevice(&dev));
+  const void* key = reinterpret_cast<const void*>(kern);
+  bool known = false;
+  for (const Memo& m : memo) known = known || (m.fn == key && m.dev == dev);
+  if (!known) {
+    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    static thread_local int next = 0;
+    memo[next] = Memo{key, dev};
+    next = (next + 1) % 8;
+  }
+  dim3 grid((max_qlen + rows - 1) / rows, n_kv, R);
+  kern<<<grid, threads, smem, st>>>(map, P);
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
 // ctas_per_sm: how many CTAs of THIS launch go on each SM (the kernel may allow more to be resident,
 // so that the CTAs of the launch after it can move in beside them).
 template <class Cfg>
@@ -514,29 +542,14 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
     if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
       return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
     // Default: the key-split kernel (32 query rows per CTA, the two halves of the key range run as two
-    // concurrent pipelines). FQB_PREFILL_TC=<groups><stages> selects the row-group kernel instead
-    // (23 = two row groups sharing 3 K/V stages, 13 / 15 = one group); both are kept for comparison.
+    // concurrent pipelines). FQB_PREFILL_TC=23 selects the row-group kernel (two row groups sharing
+    // 3 K/V stages), FQB_PREFILL_TC=13 its one-group form; both are kept for comparison.
     const char* v = std::getenv("FQB_PREFILL_TC");
-    const int variant = v ? std::atoi(v) : 93;
-    auto go = [&](auto kern, int smem, int threads, int rows) -> int {
-      FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      dim3 grid((max_qlen + rows - 1) / rows, n_kv, R);
-      kern<<<grid, threads, smem, static_cast<cudaStream_t>(stream)>>>(map, P);
-      FQB_CUDA_TRY(cudaGetLastError());
-      return FQB_OK;
-    };
-    // FQB_PREFILL_SMEM_P=1 routes P through shared memory instead of tensor memory (comparison)
-    static const bool smem_p = std::getenv("FQB_PREFILL_SMEM_P") != nullptr;
-    if (smem_p) {
-      if (variant == 13) return go(prefill_tc_kernel<1, 3, false>, TcSmem<1, 3, false>::kAlloc, TcSmem<1, 3, false>::kThreads, 32);
-      return go(prefill_tc_kernel<2, 3, false>, TcSmem<2, 3, false>::kAlloc, TcSmem<2, 3, false>::kThreads, 64);
-    }
-    if (variant == 13) return go(prefill_tc_kernel<1, 3, true>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32);
-    if (variant == 15) return go(prefill_tc_kernel<1, 5, true>, TcSmem<1, 5>::kAlloc, TcSmem<1, 5>::kThreads, 32);
-    if (variant == 24) return go(prefill_tc_kernel<2, 4, true>, TcSmem<2, 4>::kAlloc, TcSmem<2, 4>::kThreads, 64);
-    if (variant == 25) return go(prefill_tc_kernel<2, 5, true>, TcSmem<2, 5>::kAlloc, TcSmem<2, 5>::kThreads, 64);
-    if (variant == 23) return go(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64);
-    return go(prefill_tc_ks_kernel<3>, TcKsSmem<3>::kAlloc, TcKsSmem<3>::kThreads, 32);
+    const int variant = v ? std::atoi(v) : 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (variant == 23) return launch_prefill_tc(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64, max_qlen, n_kv, R, map, P, st);
+    if (variant == 13) return launch_prefill_tc(prefill_tc_kernel<1, 3, true>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32, max_qlen, n_kv, R, map, P, st);
+    return launch_prefill_tc(prefill_tc_ks_kernel<3>, TcKsSmem<3>::kAlloc, TcKsSmem<3>::kThreads, 32, max_qlen, n_kv, R, map, P, st);
   }
   constexpr int RT = 2, NS = 6, MINB = 1;
   using C = PrefillCfg<RT, NS>;
