@@ -55,6 +55,9 @@ SIGNATURES = {
     "fqb_scatter_blocks": (_i, [_p, _i, _i, _p, _i, _p, _p]),
     "fqb_device_status": (_i, [_pi]),
     "fqb_device_status_reset": (_i, []),
+    "fqb_engine_configure": (_i, [_i, _i64]),
+    "fqb_engine_status": (_i, []),
+    "fqb_engine_error": (C.c_char_p, []),
     "fqb_alloc_create": (_p, [_i]),
     "fqb_alloc_destroy": (None, [_p]),
     "fqb_alloc_num_blocks": (_i, [_p]),
@@ -86,3 +89,22 @@ def check(code, where):
     if code < 0:
         raise FqbError(code, where, lib.fqb_last_error().decode() or lib.fqb_strerror(code).decode())
     return code
+
+
+# The engine's own C++ launcher symbols (engine/src/attn_cute.h:7-20), exported by the library under
+# their Itanium-ABI names so that the engine links against them unchanged.
+ENGINE_SYMBOLS = {
+    "LaunchAttnPrefillCute": ("_ZN2fq21LaunchAttnPrefillCuteEPK13__nv_bfloat16iS2_PS0_iiiPKiS5_S5_S5_iiS5_iifP11CUstream_st",
+                              [_p, _i, _p, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
+    "LaunchAttnDecodeCute": ("_ZN2fq20LaunchAttnDecodeCuteEPK13__nv_bfloat16iS2_PS0_iiiPKiS5_S5_iS5_iifPfS6_S6_P11CUstream_st",
+                             [_p, _i, _p, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _p]),
+}
+
+
+def engine_symbol(name):
+    """The ctypes function behind one of the engine's launcher names (void return)."""
+    mangled, args = ENGINE_SYMBOLS[name]
+    fn = lib[mangled]
+    fn.restype = None
+    fn.argtypes = args
+    return fn

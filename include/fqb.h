@@ -210,6 +210,28 @@ int fqb_scatter_blocks(void* cache, int num_blocks, int kv_heads_local, const in
 int fqb_device_status(int32_t* detail /* host, may be NULL */);
 int fqb_device_status_reset(void);
 
+/* ---- the engine's launcher symbols -----------------------------------------------------------
+ * libfqb also defines, as C++ symbols with the engine's own signatures, the two attention
+ * launchers of engine/src/attn_cute.h:7-20:
+ *   void fq::LaunchAttnPrefillCute(const __nv_bfloat16* q, int q_stride, const __nv_bfloat16* cache_kv,
+ *        __nv_bfloat16* out, int n_heads, int n_kv, int head_dim, const int* pos, const int* qstart,
+ *        const int* qlen, const int* rids, int R, int max_qlen, const int* bt, int max_blocks,
+ *        int block_size, float scale, cudaStream_t s);
+ *   void fq::LaunchAttnDecodeCute(... const int* decode_rids, int n_decode, const int* bt, int max_blocks,
+ *        int block_size, float scale, float* pm, float* pl, float* pa, cudaStream_t s);
+ * so an engine built without attn_cute.cu and linked against libfqb resolves its existing calls
+ * (engine/src/model_runtime.cu:271-283) here. Those signatures carry neither the pool's block count
+ * nor the scratch size, which the kernels need for their tensor map and bounds checks:
+ * fqb_engine_configure() supplies both once, after the pool and the decode scratch are allocated
+ * (num_blocks = KvStore::NumBlocks(), engine/src/kv_store.h:37; partial_slots = the float count of
+ * pm, DecodePartialFloats(slots), engine/src/kernels.cuh:33-37). The launchers return void as the
+ * engine's do; a failed call is kept (first one wins) and fqb_engine_status() returns its code,
+ * with the message in fqb_engine_error(). Before fqb_engine_configure() they fail with
+ * FQB_ERR_STATE and launch nothing. */
+int fqb_engine_configure(int num_blocks, int64_t partial_slots);
+int fqb_engine_status(void);
+const char* fqb_engine_error(void);
+
 /* ---- host side: block allocator with prefix cache (no CUDA) ---------------------------------
  * replaces: engine/src/block_allocator.h:21-101 (class BlockAllocator) and the prefix functions
  * of engine/src/scheduler.cc:16-57. One handle = one pool of block ids [0, num_blocks);

@@ -55,3 +55,38 @@ def test_layout_and_errors_without_gpu():
     assert _lib.lib.fqb_attn_prefill(1, 6144, 1, 1, 1, 32, 7, 128, 1, 1, 1, 1, 2, 4, 1, 8, 16, 0.1, None) == -2
     assert _lib.lib.fqb_kv_append(None, 4, 8, 16, 6144, 4096, 5120, 16, 8, 16, 16, 4, None) == -1
     assert _lib.lib.fqb_kv_append(None, 4, 8, 16, 6144, 4096, 5120, 16, 8, 16, 16, 0, None) == 0
+
+
+def test_engine_launcher_symbols_are_exported_with_the_engine_signatures():
+    """The two C++ launcher names of engine/src/attn_cute.h:7-20 resolve in libfqb; where the
+    link check against the reference's own header was built, its addresses are the library's."""
+    from flashqwen_b200 import _lib
+
+    for name in _lib.ENGINE_SYMBOLS:
+        assert _lib.engine_symbol(name) is not None
+    check = os.path.join(ROOT, "oracle", "_ref", "libfq_shim_check.so")
+    if os.path.exists(check):
+        ctypes.CDLL(_lib.lib._name, mode=ctypes.RTLD_GLOBAL)
+        chk = ctypes.CDLL(check)
+        for door, name in (("shim_check_prefill", "LaunchAttnPrefillCute"), ("shim_check_decode", "LaunchAttnDecodeCute")):
+            fn = getattr(chk, door)
+            fn.restype = ctypes.c_void_p
+            want = ctypes.cast(_lib.lib[_lib.ENGINE_SYMBOLS[name][0]], ctypes.c_void_p).value
+            assert fn() == want
+
+
+def test_engine_launchers_refuse_to_run_before_configure():
+    from flashqwen_b200 import _lib
+
+    assert _lib.lib.fqb_engine_configure(0, 10) == -1
+    if _lib.lib.fqb_engine_status() == 0 and b"" == _lib.lib.fqb_engine_error():
+        # n_decode = 0 would be a no-op once configured; unconfigured it must record FQB_ERR_STATE
+        _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 128, 1, 1, 1, 0, 1, 8, 16, 0.1, 1, 1, 1, None)
+        assert _lib.lib.fqb_engine_status() == -8
+        assert b"fqb_engine_configure" in _lib.lib.fqb_engine_error()
+    assert _lib.lib.fqb_engine_configure(64, 4096) == 0
+    assert _lib.lib.fqb_engine_status() == 0
+    _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 128, 1, 1, 1, 0, 1, 8, 16, 0.1, 1, 1, 1, None)
+    assert _lib.lib.fqb_engine_status() == 0
+    _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 64, 1, 1, 1, 4, 1, 8, 16, 0.1, 1, 1, 1, None)
+    assert _lib.lib.fqb_engine_status() == -2 and b"head_dim" in _lib.lib.fqb_engine_error()
