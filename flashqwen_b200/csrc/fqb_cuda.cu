@@ -138,9 +138,6 @@ using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
-// a smaller two-head shape (three CTAs of three different launches per SM); measured slower than
-// DecodeCfg2 for independent launches, kept for comparison
-using DecodeCfg2i = DecodeCfg<2, 4, 2, 3, 256>;
 
 unsigned next_epoch() {
   static std::atomic<unsigned> counter{0x5eed0000u};
@@ -376,8 +373,6 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     const int64_t need = (decode_slots_needed(n_decode, n_kv, di.sm_count) + 3) & ~int64_t(3);
     int regions = static_cast<int>(partial_slots / need);
     if (regions > kMaxRegions) regions = kMaxRegions;
-    static const int region_cap = std::getenv("FQB_DECODE_REGIONS") ? std::atoi(std::getenv("FQB_DECODE_REGIONS")) : 0;
-    if (region_cap >= 2 && regions > region_cap) regions = region_cap;  // tuning aid
     if (regions >= 2) {
       const int region = next_region(pm, regions);
       P.pm = pm + region * need;
@@ -395,12 +390,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
         P.kvh_base = base;
         int rc, took;
         if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) {
-          static const bool small2 = std::getenv("FQB_DECODE_H2_SMALL") != nullptr;  // tuning aid
-          rc = small2 ? launch_decode<DecodeCfg2i>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st)
-                      : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st);
-          took = 2;
-        }
+        else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
         else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
