@@ -151,10 +151,21 @@ bool pdl_enabled() {
   return on;
 }
 
+// Set by fqb_attn_decode_plan: the next launch this thread makes goes out WITHOUT the programmatic
+// attribute, i.e. it starts only when the plan kernel has completed and its writes are visible. Every
+// later kernel of the step starts after that one has started, so a plan read in a prologue (before the
+// reader's own wait) is always the finished plan. Early starts alone would not give that: a kernel that
+// begins at its predecessor's trigger sees only what was visible before the predecessor began.
+thread_local bool t_plain_next = false;
+
 // Launches `kern` with or without the programmatic-serialization attribute.
 template <class... KArgs, class... Args>
 cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
                       Args... args) {
+  if (t_plain_next) {
+    pdl = false;
+    t_plain_next = false;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -322,6 +333,7 @@ int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_
   decode_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(pos, qstart, decode_rids, n_decode, max_blocks,
                                                                         plan);
   FQB_CUDA_TRY(cudaGetLastError());
+  t_plain_next = true;
   return FQB_OK;
 }
 

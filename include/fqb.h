@@ -111,9 +111,10 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
 
 /* fqb_attn_decode with flags. Every launch of this library lets the kernel after it begin early
  * (programmatic dependent launch) and itself waits for the kernel before it only after its own
- * prologue, which reads nothing but pos / qstart / decode_rids / bt -- those four arrays must not be
- * written by the kernel launched immediately before this call (the engine fills them with copies at
- * the start of the step, engine/src/model_runtime.cu:295-302).
+ * prologue, which reads nothing but pos / qstart / decode_rids / bt -- those four arrays must be final
+ * (written by copies, or by kernels that an ordinary launch has followed) before the kernel launched
+ * immediately before this call starts; the engine fills them with copies at the start of the step,
+ * engine/src/model_runtime.cu:295-302.
  *   FQB_DECODE_INDEPENDENT  the caller states that the kernel launched immediately before this call
  *       writes NOTHING this call reads (q, cache, metadata) and does not read `out`. The launch then
  *       streams KV while that kernel is still running; consecutive calls rotate through up to 64
@@ -134,7 +135,10 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
  * turns each launch's three dependent metadata loads and its scan into one coalesced load. No
  * reference counterpart (the reference recomputes per launch, engine/src/attn_cute.cu:172). The plan
  * is valid while pos / qstart / decode_rids are unchanged; at most FQB_PLAN_MAX_DECODE sequences to
- * build and 256 per planned call. Results are identical to fqb_attn_decode_ex. */
+ * build and 256 per planned call. Results are identical to fqb_attn_decode_ex. Build the plan and make
+ * the step's launches from one thread: the first launch that thread makes after
+ * fqb_attn_decode_plan waits for the plan in full (it is an ordinary launch), which is what makes the
+ * plan visible to the prologues of all later launches. */
 #define FQB_PLAN_MAX_DECODE 1024
 int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
                          int n_decode, int max_blocks, int32_t* plan, void* stream);
