@@ -692,6 +692,7 @@ def main():
         line["e2e"] = e2e
     if reference:
         line["impl"] = "reference"
+        line["ran_on_gpus"] = 1   # the reference engine is single-GPU: rank 0 runs the whole workload at every --gpus N
         line["cpu_baseline"] = {"value": round(value, 2), "unit": "GB/s", "cores": 0, "kind": "reference",
                                 "sample": "the reference has no CPU implementation of this path: its own CUDA kernels "
                                           "(kv_store.cu, attn_cute.cu rebuilt for sm_100a) on the full workload, 1 GPU"}
