@@ -6,8 +6,9 @@
 // rows (x 4 q heads = one 128-row MMA tile) and its two groups are the two HALVES OF THE KEY RANGE
 // of that same tile: each group has its own K/V ring, S tiles and O accumulator in tensor memory and
 // its own softmax warps, both run concurrently (the tensor pipe stays fed by two independent
-// pipelines), and at the end group 1 hands its (max, sum, O) to group 0 through shared memory for a
-// log-sum-exp merge. Jobs are half as long and twice as many, without any scratch in global memory.
+// pipelines), and at the end group 0 merges group 1's (max, sum) from shared memory and O straight from
+// tensor memory by log-sum-exp. Jobs are half as long and twice as many, without any scratch in global
+// memory.
 // The building blocks (descriptors, TMEM access, barriers) are those of prefill_tc.cuh; P lives in
 // tensor memory.
 #pragma once
@@ -24,18 +25,17 @@ struct TcKsSmem {
   static constexpr int kRing = STAGES * kStage;
   static constexpr int kBars = kKV + 2 * kRing;
   static constexpr int kTmemSlot = kBars + 40 * 8;
-  static constexpr int kTotal = kTmemSlot + 16;
+  static constexpr int kMl = kTmemSlot + 16;                    // group 1's {row sum, row maximum}: 2 x 128 floats
+  static constexpr int kTotal = kMl + 2 * 128 * 4;
   static constexpr int kAlloc = kTotal;                         // base must be 1024-byte aligned (checked)
   static constexpr int kThreads = 12 * 32;                      // 8 softmax, 2 TMA, S issuer, PV issuer
-  static constexpr int kMergeStride = 129;                      // floats per row of the merge buffer (no bank conflicts)
 };
 
 template <int STAGES>
 __global__ void __launch_bounds__(TcKsSmem<STAGES>::kThreads, 1)
 prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams P) {
   using L = TcKsSmem<STAGES>;
-  static_assert(STAGES == 3, "two rings of 3 x 32 KiB plus Q fill the 227 KiB; the merge buffer needs a 96 KiB ring");
-  static_assert(128 * L::kMergeStride * 4 + 1024 <= L::kRing, "the merge buffer reuses group 1's ring");
+  static_assert(STAGES == 3 && L::kTotal <= 232448, "two rings of 3 x 32 KiB plus Q fill the 227 KiB");
   constexpr int kCols = 2 * kTcGroupCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -124,7 +124,7 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
       report(FQB_ERR_TIMEOUT, kKidPrefill, what);
     }
   };
-  float* merge = reinterpret_cast<float*>(smem + L::kKV + L::kRing);  // group 1's ring, free when its MMAs are done
+  float* ml = reinterpret_cast<float*>(smem + L::kMl);
 
   if (warp < 8) {
     // =========================== softmax warps: one thread per MMA row, per key half ===========================
@@ -232,44 +232,35 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
       wait(o_done(gi, (my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1, 2000 + gi);
       tc_fence_after();
     }
-    // ---- merge the two key halves: group 1 -> shared memory -> group 0 -> out ----
-    float* mrow = merge + row * L::kMergeStride;
+    // ---- merge the two key halves ----
+    // Group 1 publishes only its row sums and maxima (shared memory); its O stays in tensor memory, where
+    // group 0's thread of the same row can read it: a warp reaches the 32 TMEM lanes of its quarter in ALL
+    // columns, and warps w and w + 4 are in the same quarter.
     if (gi == 1) {
-      mrow[128] = my_tiles > 0 ? m_used : kNegBig;
-      merge[128 * L::kMergeStride + row] = my_tiles > 0 ? l : 0.f;
-      if (my_tiles > 0) {
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          float o[16];
-          tmem_ld16(lane_addr + 128 + c * 16, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int q = 0; q < 16; ++q) mrow[c * 16 + q] = o[q];
-        }
-      }
+      ml[row] = my_tiles > 0 ? l : 0.f;
+      ml[128 + row] = my_tiles > 0 ? m_used : kNegBig;
     }
     tc_fence_before();
     asm volatile("bar.sync 1, 256;" ::: "memory");  // the 8 softmax warps only
+    tc_fence_after();
     if (gi == 0) {
-      const float m1 = mrow[128], l1 = merge[128 * L::kMergeStride + row];
+      const float l1 = ml[row], m1 = ml[128 + row];
       const float m0 = my_tiles > 0 ? m_used : kNegBig;
       const float mm = fmaxf(m0, m1);
       const float f0 = my_tiles > 0 ? fast_exp2(m0 - mm) : 0.f, f1 = l1 > 0.f ? fast_exp2(m1 - mm) : 0.f;
       const float lt = l * f0 + l1 * f1;
       const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      const bool other = g_count(1) > 0;  // same for the whole CTA
       __nv_bfloat16* orow = P.out + (static_cast<long long>(qs + qrow) * P.n_heads + kvh * kGroup + g) * kHd;
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
-        float o[16];
-        if (my_tiles > 0) {
-          tmem_ld16(lane_addr + 128 + c * 16, o);
-          tmem_wait_ld();
-        } else {
+        float o[16], o1[16];
+        if (my_tiles > 0) tmem_ld16(lane_addr + 128 + c * 16, o);
+        if (other) tmem_ld16(lane_addr + kTcGroupCols + 128 + c * 16, o1);
+        tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 16; ++q) o[q] = 0.f;
-        }
-#pragma unroll
-        for (int q = 0; q < 16; ++q) o[q] = (o[q] * f0 + (f1 > 0.f ? mrow[c * 16 + q] * f1 : 0.f)) * inv;
+        for (int q = 0; q < 16; ++q)
+          o[q] = ((my_tiles > 0 ? o[q] * f0 : 0.f) + (other && f1 > 0.f ? o1[q] * f1 : 0.f)) * inv;
         if (valid) {
           uint4 a, bq;
           a.x = pack_bf16(o[0], o[1]);    a.y = pack_bf16(o[2], o[3]);
