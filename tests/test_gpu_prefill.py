@@ -68,6 +68,18 @@ def test_ragged_requests_every_head_count(n_kv):
     assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL
 
 
+@pytest.mark.parametrize("n_req", [32, 33, 70])
+def test_many_requests_in_one_step(n_req):
+    """32 requests is the most the kernel ranks longest-first; above that it takes them in the order given."""
+    rng = np.random.default_rng(n_req)
+    hist = rng.integers(0, 200, size=n_req).tolist()
+    chunk = rng.integers(2, 40, size=n_req).tolist()
+    need = sum((h + c + 15) // 16 for h, c in zip(hist, chunk))
+    c = synth.prefill_case(hist, chunk, num_blocks=need + 4, seed=n_req, n_kv=2)
+    qkv, cache = prepared(c)
+    assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL
+
+
 def test_mixed_step_decode_and_prefill_fill_disjoint_rows():
     c = synth.prefill_case([10, 200], [40, 24], num_blocks=64, seed=60, n_kv=2, extra_decode=[50, 3, 129])
     qkv, cache = prepared(c)
