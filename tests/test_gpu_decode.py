@@ -53,6 +53,12 @@ def test_long_context_is_split_over_many_ctas_and_combined():
     assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
 
 
+def test_config4_full_size_against_the_oracle():
+    """Batch 8 at 32768 tokens each, 8 kv heads: 1 GiB of KV for one layer, every sequence cut over many CTAs."""
+    c = synth.decode_case([32768] * 8, 8 * 2048, seed=23, n_kv=8)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
 def test_batch_above_one_launch_capacity():
     rng = np.random.default_rng(5)
     lengths = rng.integers(1, 40, size=600).tolist()
