@@ -53,15 +53,22 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
   uint64_t* q_full = bars + 32;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
-  // longest request first (see prefill_tc_kernel)
+  // Longest request first (see prefill_tc_kernel). The loads that rank the requests also bring every
+  // request's row count, first row and the position of this query tile's last row, one request per lane,
+  // so once the CTA knows which request it serves nothing more has to be fetched before the block table.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int zsel = blockIdx.z;
+  const int kvh = blockIdx.y;
+  const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int q0 = qtile * kTcGroupRows;
+  int r, ql, qs, tile_last;
   if (gridDim.z > 1 && gridDim.z <= 32) {
-    int len = -1;
+    int rr = 0, n = 0, s0 = 0, len = -1, tl = -1;
     if (lane < static_cast<int>(gridDim.z)) {
-      const int rr = P.rids[lane];
-      const int n = P.qlen[rr];
-      len = n > 0 ? P.pos[P.qstart[rr] + n - 1] : -1;
+      rr = P.rids[lane];
+      n = P.qlen[rr];
+      s0 = P.qstart[rr];
+      len = n > 0 ? P.pos[s0 + n - 1] : -1;
+      tl = q0 < n ? P.pos[s0 + min(q0 + kTcGroupRows, n) - 1] : -1;
     }
     int rank = 0;
     for (int j = 0; j < static_cast<int>(gridDim.z); ++j) {
@@ -70,13 +77,17 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
     }
     const unsigned hit =
         __ballot_sync(0xffffffffu, lane < static_cast<int>(gridDim.z) && rank == static_cast<int>(blockIdx.z));
-    zsel = hit ? __ffs(hit) - 1 : static_cast<int>(blockIdx.z);
+    const int zsel = hit ? __ffs(hit) - 1 : static_cast<int>(blockIdx.z);
+    r = __shfl_sync(0xffffffffu, rr, zsel);
+    ql = __shfl_sync(0xffffffffu, n, zsel);
+    qs = __shfl_sync(0xffffffffu, s0, zsel);
+    tile_last = __shfl_sync(0xffffffffu, tl, zsel);
+  } else {
+    r = P.rids[blockIdx.z];
+    ql = P.qlen[r];
+    qs = P.qstart[r];
+    tile_last = q0 < ql ? P.pos[qs + min(q0 + kTcGroupRows, ql) - 1] : -1;
   }
-  const int r = P.rids[zsel];
-  const int kvh = blockIdx.y;
-  const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  const int ql = P.qlen[r], qs = P.qstart[r];
-  const int q0 = qtile * kTcGroupRows;
   if (q0 >= ql) return;  // before any allocation; the whole CTA leaves together
 
   if (warp == 10) {
@@ -106,7 +117,7 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  int last_pos = P.pos[qs + min(q0 + kTcGroupRows, ql) - 1];
+  int last_pos = tile_last;
   if (last_pos >= P.max_blocks * kTok) {
     if (tid == 0) report(FQB_ERR_INDEX, kKidPrefill, last_pos);
     last_pos = P.max_blocks * kTok - 1;
