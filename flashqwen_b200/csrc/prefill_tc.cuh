@@ -7,21 +7,24 @@
 //
 //   TMA warp    producer: per page and plane two 2 KiB boxes (one per 64-dim half) placed so
 //               that a 64-key K tile / V tile is a canonical 128-byte-swizzled UMMA operand
-//               ([half][key][64 dims], 8-key groups 1024 bytes apart); 2-stage ring, two CTAs per SM.
+//               ([half][key][64 dims], 8-key groups 1024 bytes apart); STAGES-deep ring of 32 KiB stages.
 //   MMA warps   one thread of each issues tcgen05.mma: the first S = Q K^T (M128 N64, 8 k-steps of 16 dims, both
 //               operands K-major) into one of two 64-column TMEM buffers, and O += P V
-//               (M128 N128, 4 k-steps of 16 keys, P K-major from shared memory, V MN-major) into
-//               a 128-column TMEM accumulator (issued by the second warp). The S issuer runs up to
-//               two tiles ahead of the softmax, so the tensor pipe works while the softmax runs; all
-//               descriptors are built once, the issue loops only add k-step offsets.
+//               (M128 N128, 4 k-steps of 16 keys, V MN-major) into a 128-column TMEM accumulator (issued by
+//               the second warp). P is the A operand either from tensor memory (TS: it overwrites the
+//               first 32 columns of its S tile as bf16 pairs) or from a swizzled shared-memory tile.
+//               The S issuer runs up to two tiles ahead of the softmax, so the tensor pipe works while the
+//               softmax runs; all descriptors are built once, the issue loops only add k-step offsets.
 //   warps 0-3 (and 4-7 with two row groups per CTA)
 //               softmax: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, scale,
-//               causal mask, running max without any shuffle, exp2, P -> bf16 into shared memory.
+//               causal mask, running max without any shuffle, exp2, P -> bf16.
 //               The accumulator is rescaled in TMEM only when a row's max grew by more than 2^8
 //               since the scale in use (the probabilities stay exact relative to that scale).
 // Completion is tracked with mbarriers (tcgen05.commit for MMA groups); every wait is bounded and
-// ends in a status code. TMEM (256 columns per CTA, two CTAs per SM use all 512) is allocated by
-// warp 5 and freed before exit.
+// ends in a status code. A kernel that allocates tensor memory runs one CTA per SM here; the CTA
+// allocates 256 columns per row group and frees them before exit.
+// This file also holds the building blocks (descriptors, TMEM access, fences) that the key-split
+// kernel in prefill_tc_ks.cuh, the default, is made of.
 #pragma once
 
 #include "common.cuh"
