@@ -598,8 +598,12 @@ def main():
         d2h = w.h_out.numel() * w.h_out.element_size()
 
         copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        group = 6  # layers per copy chunk: copies of chunk i+1 overlap the kernels of chunk i
-        chunks = [(l0, min(a.layers, l0 + group)) for l0 in range(0, a.layers, group)]
+        # layers per copy chunk: copies of chunk i+1 overlap the kernels of chunk i; the first and the last
+        # chunk are one layer, so that the first kernel waits for little and little is left to copy back
+        # after the last one
+        group = 6
+        cuts = sorted(set([0, min(1, a.layers)] + list(range(group, a.layers, group)) + [max(a.layers - 1, 0), a.layers]))
+        chunks = [(l0, l1) for l0, l1 in zip(cuts[:-1], cuts[1:]) if l1 > l0]
         ev_in = [torch.cuda.Event() for _ in chunks]
         ev_out = [torch.cuda.Event() for _ in chunks]
 
@@ -660,7 +664,7 @@ def main():
         check()
         e2e = {"value": round(w.bytes_layer_total * a.layers / (ms_e * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(ms_e, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "includes": "H2D of qkv rows + metadata (chunks of 6 layers on a copy stream), per-layer KV append + decode attention"
+               "includes": "H2D of qkv rows + metadata (chunks of up to 6 layers on a copy stream, first and last chunk one layer), per-layer KV append + decode attention"
                            + (", one NCCL all-gather of all layers' head outputs" if dist_on else "") + ", D2H of the output"
                            + ("; one CUDA graph per step, host sync every step" if a.graph else "")}
 
