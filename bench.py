@@ -68,7 +68,10 @@ def parse():
                          "histories 0/1024/3000/7000). copy: prefix-block copy-on-write copies over 36 layers")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="tuning aid: run rank 0's share of an N-way kv-head shard on this one GPU")
-    return ap.parse_args()
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)   # never time a cold loop: at least 3 untimed steps, reported as run
+    a.steps = max(a.steps, 1)
+    return a
 
 
 class ClockSampler:
