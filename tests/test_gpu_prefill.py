@@ -80,6 +80,21 @@ def test_many_requests_in_one_step(n_req):
     assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL
 
 
+@pytest.mark.parametrize("env", [{"FQB_PREFILL_TC": "77"}, {"FQB_PREFILL_TC": "23"}, {"FQB_PREFILL_TC": "13"},
+                                 {"FQB_PREFILL": "mma"}])
+def test_the_selectable_kernels_match_the_oracle_too(env, monkeypatch):
+    """The library reads FQB_PREFILL / FQB_PREFILL_TC at every call: the kernels kept beside the default
+    one (deep pipeline, row groups, one group, mma.sync) get the same ragged, mixed and long cases."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    for hist, chunk, n_kv, seed in (([0, 40, 100, 333], [20, 16, 33, 70], 2, 71), ([1000, 31], [100, 97], 1, 72),
+                                    ([0], [2], 4, 73), ([2500], [300], 8, 74)):
+        need = sum((h + c + 15) // 16 for h, c in zip(hist, chunk))
+        c = synth.prefill_case(hist, chunk, num_blocks=need + 5, seed=seed, n_kv=n_kv)
+        qkv, cache = prepared(c)
+        assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL, (env, hist)
+
+
 def test_mixed_step_decode_and_prefill_fill_disjoint_rows():
     c = synth.prefill_case([10, 200], [40, 24], num_blocks=64, seed=60, n_kv=2, extra_decode=[50, 3, 129])
     qkv, cache = prepared(c)
