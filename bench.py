@@ -246,7 +246,7 @@ def fqb_runner(w):
 
 
 def ref_runner(w):
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle_lib
 
     ref = oracle_lib.ref_cuda()
@@ -299,7 +299,7 @@ def time_region(fn, steps, warmup, dist_on, dev):
 def cpu_oracle_rate(w, a, budget_s=20.0):
     """Times the scalar oracle (all host threads) on a bounded sample of the same workload: whole
     layers of the full batch, all 32 heads, as many layers as fit in about `budget_s` seconds."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle_lib as O
 
     cores = O.hardware_threads()
@@ -390,7 +390,7 @@ def run_cfg3(a, dev):
     scale = HD ** -0.5
     reference = a.impl == "reference"
     if reference:
-        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import oracle_lib
         ref = oracle_lib.ref_cuda()
         if ref is None:

@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["csrc/fqb_cuda.cu", "csrc/host/errors.cc", "csrc/host/allocator.cc", "csrc/host/layout.cc", "csrc/host/engine_shim.cc"]
-HEADERS = ["csrc/common.cuh", "csrc/decode.cuh", "csrc/prefill.cuh", "csrc/prefill_tc.cuh", "csrc/prefill_tc_ks.cuh", "csrc/prefill_tc_deep.cuh", "csrc/kv_append.cuh", "csrc/blocks.cuh",
+HEADERS = ["csrc/common.cuh", "csrc/decode.cuh", "csrc/umma.cuh", "csrc/prefill_tc_ks.cuh", "csrc/kv_append.cuh", "csrc/blocks.cuh",
            "csrc/errors.h", "../include/fqb.h"]
 
 

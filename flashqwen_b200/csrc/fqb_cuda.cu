@@ -1,6 +1,7 @@
 // libfqb, CUDA side: the extern "C" operators declared in include/fqb.h. Host code here only
 // validates scalar arguments, builds the TMA descriptor of the cache and enqueues kernels on the
 // caller's stream; it allocates nothing and never synchronises (fqb_device_status excepted).
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -13,10 +14,7 @@
 #include "decode.cuh"
 #include "errors.h"
 #include "kv_append.cuh"
-#include "prefill.cuh"
-#include "prefill_tc.cuh"
 #include "prefill_tc_ks.cuh"
-#include "prefill_tc_deep.cuh"
 
 namespace fqb {
 namespace {
@@ -147,9 +145,13 @@ unsigned next_epoch() {
   return e;
 }
 
-bool pdl_enabled() {
-  static const bool on = std::getenv("FQB_NO_PDL") == nullptr;  // FQB_NO_PDL=1: plain launches (debugging aid)
-  return on;
+// Building with -DFQB_NO_PDL turns every launch into a plain one (debugging aid).
+constexpr bool pdl_enabled() {
+#ifdef FQB_NO_PDL
+  return false;
+#else
+  return true;
+#endif
 }
 
 // Set by fqb_attn_decode_plan: the next launch this thread makes goes out WITHOUT the programmatic
@@ -180,30 +182,20 @@ cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-// One launcher for the tcgen05 prefill kernels: opts the kernel in to its dynamic shared memory once
-// per device and thread, then launches (query tiles, kv heads, requests).
-template <class Kern>
-int launch_prefill_tc(Kern kern, int smem, int threads, int rows, int max_qlen, int n_kv, int R, const CUtensorMap& map,
-                      const PrefillParams& P, cudaStream_t st) {
-  // the kernels share one function-pointer type, so the "already opted in" memo is keyed by pointer
-  struct Memo {
-    const void* fn;
-    int dev;
-  };
-  static thread_local Memo memo[8] = {};
+// Opts the prefill kernel in to its dynamic shared memory once per device and thread, then launches
+// (query tiles of 32 rows, kv heads, requests).
+int launch_prefill(int max_qlen, int n_kv, int R, const CUtensorMap& map, const PrefillParams& P, cudaStream_t st) {
+  using L = TcKsSmem<3>;
+  auto kern = prefill_tc_ks_kernel<3>;
+  static thread_local int attr_dev = -1;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
-  const void* key = reinterpret_cast<const void*>(kern);
-  bool known = false;
-  for (const Memo& m : memo) known = known || (m.fn == key && m.dev == dev);
-  if (!known) {
-    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    static thread_local int next = 0;
-    memo[next] = Memo{key, dev};
-    next = (next + 1) % 8;
+  if (attr_dev != dev) {
+    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    attr_dev = dev;
   }
-  dim3 grid((max_qlen + rows - 1) / rows, n_kv, R);
-  kern<<<grid, threads, smem, st>>>(map, P);
+  dim3 grid((max_qlen + kTcGroupRows - 1) / kTcGroupRows, n_kv, R);
+  kern<<<grid, L::kThreads, L::kAlloc, st>>>(map, P);
   FQB_CUDA_TRY(cudaGetLastError());
   return FQB_OK;
 }
@@ -351,6 +343,8 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     return set_error(FQB_ERR_INVALID, "attn_decode: null pointer");
   if (num_blocks <= 0 || max_blocks <= 0 || partial_slots <= 0)
     return set_error(FQB_ERR_INVALID, "attn_decode: non-positive size");
+  if (!(scale > 0.f) || !std::isfinite(scale))
+    return set_error(FQB_ERR_INVALID, "attn_decode: the softmax scale must be positive and finite");
   if (!aligned16(q) || !aligned16(cache) || !aligned16(out) || !aligned16(pa) || (q_stride % 8) ||
       (reinterpret_cast<uintptr_t>(pl) & 7u) || (reinterpret_cast<uintptr_t>(pm) & 3u))
     return set_error(FQB_ERR_INVALID, "attn_decode: q, cache, out, pa and q_stride must keep 16-byte alignment, pl 8");
@@ -516,15 +510,14 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
     return set_error(FQB_ERR_INVALID, "attn_prefill: null pointer");
   if (num_blocks <= 0 || max_blocks <= 0 || max_qlen <= 0)
     return set_error(FQB_ERR_INVALID, "attn_prefill: non-positive size");
-  if ((reinterpret_cast<uintptr_t>(q) & 3u) || !aligned16(cache) || (reinterpret_cast<uintptr_t>(out) & 3u) ||
-      (q_stride % 2))
-    return set_error(FQB_ERR_INVALID, "attn_prefill: misaligned pointer or stride");
+  if (!aligned16(cache)) return set_error(FQB_ERR_INVALID, "attn_prefill: misaligned cache pointer");
+  if (!(scale > 0.f) || !std::isfinite(scale))
+    return set_error(FQB_ERR_INVALID, "attn_prefill: the softmax scale must be positive and finite");
   if (n_kv > 65535 || R > 65535) return set_error(FQB_ERR_SHAPE, "attn_prefill: n_kv or R above 65535");
-  // FQB_PREFILL=mma selects the mma.sync kernel (kept for comparison); the default is the tcgen05 one
-  const char* sel = std::getenv("FQB_PREFILL");
-  const bool use_tc = !(sel && sel[0] == 'm');
+  if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
+    return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
   CUtensorMap map;
-  if (int rc = make_cache_map(cache, num_blocks, n_kv, map, use_tc)) return rc;
+  if (int rc = make_cache_map(cache, num_blocks, n_kv, map, true)) return rc;
   PrefillParams P;
   P.q = static_cast<const __nv_bfloat16*>(q);
   P.q_stride = q_stride;
@@ -539,36 +532,7 @@ int fqb_attn_prefill(const void* q, int q_stride, const void* cache, int num_blo
   P.max_blocks = max_blocks;
   P.num_blocks = num_blocks;
   P.scale_log2 = scale * kLog2e;
-  int dev = 0;
-  FQB_CUDA_TRY(cudaGetDevice(&dev));
-  if (use_tc) {
-    if (!aligned16(q) || !aligned16(out) || (q_stride % 8))
-      return set_error(FQB_ERR_INVALID, "attn_prefill: q, out and q_stride must keep 16-byte alignment");
-    // Default: the key-split kernel (32 query rows per CTA, the two halves of the key range run as two
-    // concurrent pipelines). FQB_PREFILL_TC=77 selects the deep-pipeline kernel (one 128-row tile per CTA,
-    // 128-key tiles, three S buffers: 2-3 % faster on long histories, 12 % slower on one-tile jobs),
-    // FQB_PREFILL_TC=23 the row-group kernel (two row groups sharing 3 K/V stages), FQB_PREFILL_TC=13 its
-    // one-group form; all are parity-tested and kept for comparison.
-    const char* v = std::getenv("FQB_PREFILL_TC");
-    const int variant = v ? std::atoi(v) : 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (variant == 77) return launch_prefill_tc(prefill_tc_deep_kernel, TcDeepSmem::kAlloc, TcDeepSmem::kThreads, 32, max_qlen, n_kv, R, map, P, st);
-    if (variant == 23) return launch_prefill_tc(prefill_tc_kernel<2, 3, true>, TcSmem<2, 3>::kAlloc, TcSmem<2, 3>::kThreads, 64, max_qlen, n_kv, R, map, P, st);
-    if (variant == 13) return launch_prefill_tc(prefill_tc_kernel<1, 3, true>, TcSmem<1, 3>::kAlloc, TcSmem<1, 3>::kThreads, 32, max_qlen, n_kv, R, map, P, st);
-    return launch_prefill_tc(prefill_tc_ks_kernel<3>, TcKsSmem<3>::kAlloc, TcKsSmem<3>::kThreads, 32, max_qlen, n_kv, R, map, P, st);
-  }
-  constexpr int RT = 2, NS = 6, MINB = 1;
-  using C = PrefillCfg<RT, NS>;
-  auto kern = prefill_kernel<RT, NS, MINB>;
-  static thread_local int attr_dev = -1;
-  if (attr_dev != dev) {
-    FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr_dev = dev;
-  }
-  dim3 grid((max_qlen + C::kBM - 1) / C::kBM, n_kv, R);
-  kern<<<grid, C::kThreads, C::kSmem, static_cast<cudaStream_t>(stream)>>>(map, P);
-  FQB_CUDA_TRY(cudaGetLastError());
-  return FQB_OK;
+  return launch_prefill(max_qlen, n_kv, R, map, P, static_cast<cudaStream_t>(stream));
 }
 
 static int block_move(void* const* layers, int n_layers, void* cache, void* lin, int num_blocks,

@@ -1,21 +1,57 @@
-// Kernel 3, key-split form of the tcgen05 / TMEM prefill kernel.
+// Kernel 3: chunked-prefill paged attention on tcgen05 / tensor memory, key-split form.
 //
-// prefill_tc_kernel gives each CTA 64 query rows as two row groups that share K/V stages; its jobs
-// are as long as the request's whole key range, and with skewed histories (one request at 7000
-// cached tokens beside one at 0) the longest jobs decide the run time. Here a CTA takes 32 query
-// rows (x 4 q heads = one 128-row MMA tile) and its two groups are the two HALVES OF THE KEY RANGE
-// of that same tile: each group has its own K/V ring, S tiles and O accumulator in tensor memory and
-// its own softmax warps, both run concurrently (the tensor pipe stays fed by two independent
-// pipelines), and at the end group 0 merges group 1's (max, sum) from shared memory and O straight from
-// tensor memory by log-sum-exp. Jobs are half as long and twice as many, without any scratch in global
-// memory.
-// The building blocks (descriptors, TMEM access, barriers) are those of prefill_tc.cuh; P lives in
-// tensor memory.
+// Operator semantics follow the reference's CutePrefillKernel / LaunchAttnPrefillCute
+// (engine/src/attn_cute.cu:30-163 of the FlashQwen tree): rows of one request are contiguous, row i
+// sees key positions <= pos[qstart+i], the scale is applied after Q K^T, probabilities are rounded to
+// bf16 before P V, bf16 output at out[(row*n_heads + h)*128 + d]. The design is not the reference's:
+//
+//   * One CTA = 32 query rows x the 4 query heads of one kv head = one 128-row MMA tile
+//     (row = head * 32 + query row); keys are consumed 64 at a time (4 pages). The CTA's two warp
+//     groups take the two HALVES OF THE KEY RANGE of that tile: each group has its own K/V ring, S
+//     tiles and O accumulator in tensor memory and its own softmax warps, both run concurrently (the
+//     tensor pipe stays fed by two independent pipelines), and at the end group 0 merges group 1's
+//     (max, sum) from shared memory and its O straight out of tensor memory by log-sum-exp. With
+//     skewed histories (one request at 7000 cached tokens beside one at 0) the longest jobs decide the
+//     run time; the split halves them without any scratch in global memory.
+//   * TMA warps (one per half): per page and plane two 2 KiB boxes (one per 64-dim half) placed so
+//     that a 64-key K tile / V tile is a canonical 128-byte-swizzled UMMA operand
+//     ([half][key][64 dims], 8-key groups 1024 bytes apart); 3-deep ring of 32 KiB stages per half.
+//   * One thread issues S = Q K^T (M128 N64, 8 k-steps of 16 dims, both operands K-major) into one of
+//     two 64-column TMEM buffers per half; another issues O += P V (M128 N128, 4 k-steps of 16 keys,
+//     V MN-major) with P read from tensor memory: the softmax overwrites the first 32 columns of its
+//     S tile with packed bf16 pairs.
+//   * Softmax warps: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, causal mask,
+//     running max without any shuffle, exp2, P -> bf16. The accumulator is rescaled in TMEM only
+//     when a row's max grew by more than 2^8 since the scale in use (the probabilities stay exact
+//     relative to that scale).
+// Completion is tracked with mbarriers (tcgen05.commit for MMA groups); every wait is bounded and
+// ends in a status code. A kernel that allocates tensor memory runs one CTA per SM here; the CTA
+// allocates 512 columns and frees them before exit.
 #pragma once
 
-#include "prefill_tc.cuh"
+#include <cmath>
+
+#include "umma.cuh"
 
 namespace fqb {
+
+struct PrefillParams {
+  const __nv_bfloat16* q;
+  int q_stride;
+  __nv_bfloat16* out;
+  int n_heads, n_kv;
+  const int* pos;
+  const int* qstart;
+  const int* qlen;
+  const int* rids;
+  const int* bt;
+  int max_blocks, num_blocks;
+  float scale_log2;  // softmax scale * log2(e), > 0
+};
+
+constexpr int kTcGroupRows = 32;  // query rows per CTA (x 4 q heads = one 128-row MMA tile)
+constexpr int kTcBN = 64;         // keys per tile
+constexpr int kTcGroupCols = 256; // TMEM columns per key half: S0 [0,64), S1 [64,128), O [128,256)
 
 template <int STAGES>
 struct TcKsSmem {
@@ -53,9 +89,13 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
   uint64_t* q_full = bars + 32;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
 
-  // Longest request first (see prefill_tc_kernel). The loads that rank the requests also bring every
-  // request's row count, first row and the position of this query tile's last row, one request per lane,
-  // so once the CTA knows which request it serves nothing more has to be fetched before the block table.
+  // Longest jobs first: CTAs are handed out in blockIdx order (x fastest, z slowest), a job's length is
+  // its last visible key position, and one CTA per SM runs at a time, so the z-th CTA plane takes the
+  // request with the z-th longest key range (ranked here on the device; up to 32 requests, more keep
+  // their given order) and x walks its query tiles from the last one down. The loads that rank the
+  // requests also bring every request's row count, first row and the position of this query tile's last
+  // row, one request per lane, so once the CTA knows which request it serves nothing more has to be
+  // fetched before the block table.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kvh = blockIdx.y;
   const int qtile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
@@ -172,12 +212,19 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
       for (int c = 0; c < 4; ++c) tmem_ld16(lane_addr + b * 64 + c * 16, x + c * 16);
       tmem_wait_ld();
       const int k0 = k * kTcBN;
+      // Keys this row may not see get a score of -inf, so their probability is exactly 0 whatever the
+      // scale: ex2(fma(-inf, scale, -m)) = 0. A tile in which the row sees no key at all (the upper key
+      // half of a row near the start of the chunk) then leaves the row's maximum, sum and O untouched:
+      // its tile maximum is -inf, m_used stays the finite value it had (at least kNegBig), nothing grows.
+      // (Masking with a large finite number instead goes wrong exactly there: the maximum in use
+      // becomes the rounded product of that number and the scale, and the exponent of a masked key the
+      // rounding residue of the same product, about +-1e21 -- inf for half of all scales.)
       if (k0 + kTcBN - 1 > qp) {
 #pragma unroll
         for (int j = 0; j < kTcBN; ++j)
-          if (k0 + j > qp) x[j] = kNegBig;
+          if (k0 + j > qp) x[j] = -INFINITY;
       }
-      float mx0 = kNegBig, mx1 = kNegBig, mx2 = kNegBig, mx3 = kNegBig;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int j = 0; j < kTcBN; j += 4) {
         mx0 = fmaxf(mx0, x[j]);

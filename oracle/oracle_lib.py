@@ -1,6 +1,6 @@
 """ctypes access to the test oracle (oracle/libfq_oracle.so) and, when built, to the reference's
 own code compiled in place (oracle/_ref/). Test infrastructure: imported from tests/, smoke()
-and bench.py's CPU-baseline leg only."""
+and bench.py's CPU-baseline and reference arms only -- never by the flashqwen_b200 package."""
 import ctypes as C
 import os
 import subprocess

@@ -48,6 +48,16 @@ def test_ragged_batch_every_head_count(n_kv):
     assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
 
 
+@pytest.mark.parametrize("scale", [128 ** -0.5, float(np.nextafter(np.float32(128 ** -0.5), np.float32(0))), 0.1, 0.125,
+                                   0.05, 0.3, 1.0])
+def test_any_softmax_scale(scale):
+    c = synth.decode_case([1, 15, 16, 17, 100, 257, 1500, 33], 160, seed=40, n_kv=2, shuffle_rids=True)
+    c.scale = scale
+    got = run_decode(c)
+    assert np.isfinite(synth.bf16_to_f32(got)).all()
+    assert maxabs(got, oracle_decode(c)) <= TOL
+
+
 def test_long_context_is_split_over_many_ctas_and_combined():
     c = synth.decode_case([20000, 3], 1400, seed=21, n_kv=1)
     assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
@@ -95,9 +105,10 @@ def test_scratch_contents_do_not_matter_between_calls():
 
 
 def test_reference_sized_scratch_is_enough():
-    # the engine gives slots*64*16 floats (engine/src/kernels.cuh:33-37), slots = 32 by default
-    c = synth.decode_case([4000] * 4, 1100, seed=26, n_kv=8)
-    s = Scratch(4, c.n_heads, c.max_blocks, slots=32 * 64 * 16)
+    # the engine gives DecodePartialFloats(slots) = slots*64*16 floats (engine/src/kernels.cuh:33-37) and
+    # slots defaults to 16 (engine/src/args.h:14): 16 384 floats, with at most 16 sequences per step
+    c = synth.decode_case([4000, 3000, 17, 2500] * 4, 2600, seed=26, n_kv=8)
+    s = Scratch(16, c.n_heads, c.max_blocks, slots=16 * 64 * 16)
     assert maxabs(run_decode(c, scratch=s), oracle_decode(c)) <= TOL
 
 

@@ -80,19 +80,33 @@ def test_many_requests_in_one_step(n_req):
     assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL
 
 
-@pytest.mark.parametrize("env", [{"FQB_PREFILL_TC": "77"}, {"FQB_PREFILL_TC": "23"}, {"FQB_PREFILL_TC": "13"},
-                                 {"FQB_PREFILL": "mma"}])
-def test_the_selectable_kernels_match_the_oracle_too(env, monkeypatch):
-    """The library reads FQB_PREFILL / FQB_PREFILL_TC at every call: the kernels kept beside the default
-    one (deep pipeline, row groups, one group, mma.sync) get the same ragged, mixed and long cases."""
-    for k, v in env.items():
-        monkeypatch.setenv(k, v)
-    for hist, chunk, n_kv, seed in (([0, 40, 100, 333], [20, 16, 33, 70], 2, 71), ([1000, 31], [100, 97], 1, 72),
-                                    ([0], [2], 4, 73), ([2500], [300], 8, 74)):
-        need = sum((h + c + 15) // 16 for h, c in zip(hist, chunk))
-        c = synth.prefill_case(hist, chunk, num_blocks=need + 5, seed=seed, n_kv=n_kv)
+SCALES = [128 ** -0.5, float(np.nextafter(np.float32(128 ** -0.5), np.float32(0))), 0.1, 0.125, 0.05, 0.3, 1.0]
+
+
+@pytest.mark.parametrize("scale", SCALES)
+def test_any_softmax_scale_with_rows_that_see_nothing_of_the_upper_key_half(scale):
+    """The CTA's second warp group takes the upper half of the key tiles. Rows at the start of a query
+    tile whose positions lie below that half see none of its keys (history 60 + chunk 20: positions
+    60..63 against keys 64..127). Such a tile must leave the row untouched for every scale, not only
+    for 1/sqrt(128)."""
+    for hist, chunk, seed in ((60, 20, 1), (0, 70, 2), (130, 10, 3), (120, 20, 4), (50, 32, 5), (185, 30, 6),
+                              (1000, 40, 7)):
+        c = synth.prefill_case([hist], [chunk], num_blocks=(hist + chunk) // 16 + 3, seed=900 + seed, n_kv=2)
+        c.scale = scale
         qkv, cache = prepared(c)
-        assert maxabs(run_prefill(c, dv(cache), dv(qkv)), oracle_prefill(c, qkv, cache)) <= TOL, (env, hist)
+        got = run_prefill(c, dv(cache), dv(qkv))
+        assert np.isfinite(synth.bf16_to_f32(got)).all(), (scale, hist, chunk)
+        assert maxabs(got, oracle_prefill(c, qkv, cache)) <= TOL, (scale, hist, chunk)
+
+
+def test_a_scale_that_is_not_positive_is_refused():
+    c = synth.prefill_case([0], [8], num_blocks=4, seed=1, n_kv=1)
+    qkv, cache = prepared(c)
+    for bad in (0.0, -0.1, float("nan"), float("inf")):
+        c.scale = bad
+        with pytest.raises(fq.FqbError) as e:
+            run_prefill(c, dv(cache), dv(qkv))
+        assert e.value.code == -1
 
 
 def test_mixed_step_decode_and_prefill_fill_disjoint_rows():

@@ -24,6 +24,7 @@ def _worker(rank, world, port, q):
     here = os.path.dirname(os.path.abspath(__file__))
     sys.path.insert(0, here)
     sys.path.insert(0, os.path.dirname(here))
+    sys.path.insert(0, os.path.join(os.path.dirname(here), "oracle"))
     import flashqwen_b200 as fq
     import oracle_lib as O
     from flashqwen_b200 import synth
