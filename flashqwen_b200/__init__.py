@@ -9,8 +9,10 @@ operator raises if the library is missing.
 from ._lib import FqbError, lib, library_path  # noqa: F401
 from .host import BlockAllocator, acquire_prefix, cache_blocks, cow_prepare, hash_block, step_pack  # noqa: F401
 from .ops import (  # noqa: F401
+    DECODE_HISTORY_STABLE,
     DECODE_INDEPENDENT,
     KvStore,
+    append_attn_decode,
     attn_decode,
     attn_decode_plan,
     attn_decode_planned,

@@ -41,12 +41,15 @@ SIGNATURES = {
     "fqb_kv_append": (_i, [_p, _i, _i, _p, _i, _i, _i, _p, _i, _p, _p, _i, _p]),
     "fqb_norm_rope_append": (_i, [_p, _i, _i, _i, _p, _i, _i, _i, _i, _p, _p, _p, _p, _f, _p, _i, _p, _p, _i, _p]),
     "fqb_attn_decode_partial_slots": (_i64, [_i, _i, _i]),
+    "fqb_attn_decode_slots_needed": (_i64, [_i, _i]),
     "fqb_attn_decode": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64, _p]),
     "fqb_attn_decode_ex": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64,
                                 C.c_uint, _p]),
     "fqb_attn_decode_plan": (_i, [_p, _p, _p, _i, _i, _p, _p]),
     "fqb_attn_decode_planned": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64, C.c_uint,
                                      _p]),
+    "fqb_append_attn_decode": (_i, [_p, _i, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p,
+                                    _i64, C.c_uint, _p]),
     "fqb_attn_decode_static": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
     "fqb_attn_prefill": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
     "fqb_copy_blocks": (_i, [_p, _i, _i, _p, _i, _p]),

@@ -1,4 +1,5 @@
-// Kernel 2: GQA-shared split-K paged decode attention with the log-sum-exp combine fused in.
+// Kernel 2: GQA-shared split-K paged decode attention with the log-sum-exp combine fused in, and
+// optionally the KV append of the step's new token fused in as well.
 //
 // Operator semantics follow the reference's LaunchAttnDecodeCute
 // (engine/src/attn_cute.cu:165-261 of the FlashQwen tree): decode sequence di attends keys
@@ -6,23 +7,28 @@
 // out[(flat*n_heads + h)*128 + d]. The design is not the reference's:
 //
 //   * Work is the flat list of pages of all sequences (sequence-major). It is cut into equal
-//     contiguous page ranges, one per persistent CTA, on the device from the actual context
-//     lengths -- the grid depends only on the SM count, so the launch can sit in a CUDA graph
-//     while lengths change. A CTA handles every local kv head of its pages: warp w serves head
-//     w % HEADS, so the loads a CTA has in flight cover whole 64 KiB pages (all heads of K and V
-//     are adjacent in memory), not isolated 256-byte rows.
+//     contiguous SEGMENTS, one per (CTA, warp group) of a persistent grid, on the device from the
+//     actual context lengths -- the grid depends only on the SM count, so the launch can sit in a
+//     CUDA graph while lengths change. Warp w serves kv head w % HEADS of segment
+//     blockIdx.x * SUB + w / HEADS: with all local heads in one CTA (HEADS == NW) the loads a CTA has
+//     in flight cover whole 64 KiB pages (all heads of K and V are adjacent in memory); with one or
+//     two local heads the SUB warps that share a head take neighbouring segments.
 //   * Each warp owns a private ring of NS page buffers (8 KiB: K and V rows of one head of one
 //     16-token page) filled by single-thread TMA tensor loads (5-D box, 128-byte swizzle) that
 //     complete on the ring's mbarriers. The warp that consumes a buffer refills it, so the stream
-//     has no cross-warp handshake and runs ahead across sequence boundaries. With all 8 kv heads
-//     local (HEADS == NW) a warp never synchronises with another warp at all.
+//     has no cross-warp handshake and no block barrier at all, and runs ahead across sequence
+//     boundaries.
 //   * Scores and PV products use mma.sync m16n8k16 with the 4 query heads as rows 0..3 of the
 //     16-row A tile (rows 4..15 are zero padding): S[4x16] = Q[4x128] K^T, O[4x128] += P[4x16] V.
 //     The query rows of the next sequence are fetched into registers while the current one runs.
-//   * A (sequence, head) pair that lies inside one CTA is normalised and written straight to
-//     `out`. A pair cut by CTA boundaries leaves one unnormalised partial per CTA and takes a
+//   * A (sequence, head) pair that lies inside one segment is normalised and written straight to
+//     `out`. A pair cut by segment boundaries leaves one unnormalised partial per segment and takes a
 //     ticket on the pair's arrival counter; the warp that takes the last ticket merges the
 //     partials (log-sum-exp) and writes `out` -- no second kernel, no inter-CTA waiting.
+//   * Fused append (the step's new token, engine/src/kv_store.cu:48-75): exactly one warp per
+//     (sequence, head) streams the sequence's last page; it copies the new K and V rows from the
+//     fused qkv row into the cache and into the page buffer it has just received, so the token takes
+//     part in the attention without a separate append kernel in front.
 #pragma once
 
 #include "common.cuh"
@@ -47,20 +53,33 @@ struct DecodeParams {
   long long partial_slots;
   unsigned epoch;  // differs from launch to launch, never 0
   int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
-  int independent; // 1: nothing this launch reads is written by the kernel launched before it
+  int mode;        // kDecodeWaitFirst / kDecodeNoWait / kDecodeWaitRows, see below
   int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
   const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
+  // fused append of the new token (cache_w == nullptr: none). The rows are qkv + flat * q_stride
+  // seen from q: K of cache head kvh at q + k_rel + kvh*128, V at q + v_rel + kvh*128.
+  __nv_bfloat16* cache_w;
+  long long k_rel, v_rel;
 };
 
-// Scratch layout. Partial (sequence di, CTA b, kv head, q head g) lives at slot
+// What a launch waits for before it touches anything but the step metadata:
+//   kDecodeWaitFirst  the kernel launched before it has completed (always safe);
+//   kDecodeNoWait     nothing: that kernel writes nothing this launch reads (the wait moves to the very
+//                     end, where it only keeps kernels completing in order);
+//   kDecodeWaitRows   the page ring is filled first -- that kernel writes none of the cached keys
+//                     0..qpos-1 -- and only then the launch waits, before it reads the q / K / V rows of
+//                     the step, which that kernel may have produced.
+enum { kDecodeWaitFirst = 0, kDecodeNoWait = 1, kDecodeWaitRows = 2 };
+
+// Scratch layout. Partial (sequence di, segment b, kv head, q head g) lives at slot
 // ((di + b) * n_kv + kvh) * 4 + g of pm / pl / pa: along the flat page list the cuts are sequence
-// boundaries and CTA boundaries, so di + b numbers the segments uniquely. The arrival counters
+// boundaries and segment boundaries, so di + b numbers the pieces uniquely. The arrival counters
 // (one 64-bit word per (sequence, kv head)) sit at the end of pl.
 __host__ __device__ inline long long decode_counter_base(long long partial_slots, int n_pairs) {
   return (partial_slots - 2LL * n_pairs) & ~1LL;  // float index into pl, 8-byte aligned
 }
-__host__ __device__ inline long long decode_slots_needed(int n_decode, int n_kv, int grid) {
-  return (static_cast<long long>(n_decode) + grid) * n_kv * kGroup + 2LL * n_decode * n_kv + 2;
+__host__ __device__ inline long long decode_slots_needed(int n_decode, int n_kv, int segments) {
+  return (static_cast<long long>(n_decode) + segments) * n_kv * kGroup + 2LL * n_decode * n_kv + 2;
 }
 
 // Takes a ticket on an arrival counter {epoch : 32 | count : 32}. A word whose epoch field is not
@@ -84,10 +103,7 @@ template <int NW, int NS, int MAXD>
 struct DecodeSmem {
   static constexpr int kStageBytes = NW * NS * kPageBytes;
   static constexpr int kBarOff = kStageBytes;
-  static constexpr int kMoOff = kBarOff + NW * NS * 8;
-  static constexpr int kMmOff = kMoOff + NW * kGroup * kHd * 4;
-  static constexpr int kMlOff = kMmOff + NW * kGroup * 4;
-  static constexpr int kROff = kMlOff + NW * kGroup * 4;
+  static constexpr int kROff = kBarOff + NW * NS * 8;
   static constexpr int kFlatOff = kROff + MAXD * 4;
   static constexpr int kQposOff = kFlatOff + MAXD * 4;
   static constexpr int kCumOff = kQposOff + MAXD * 4;
@@ -95,7 +111,7 @@ struct DecodeSmem {
   static constexpr int kAlloc = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
-// An item is a maximal run of pages of one sequence inside a CTA's page range.
+// An item is a maximal run of pages of one sequence inside a segment.
 struct ItemCursor {
   int off;     // flat page offset of the item's first page; >= hi when exhausted
   int di;
@@ -117,26 +133,44 @@ __device__ __forceinline__ void item_at(ItemCursor& c, int off, int hi, int n_de
   c.pe = min(c.np, c.pb + (hi - off));
 }
 
-// Merges the partials of pair (di, kvh) left by CTAs b0..b1 and writes the 4 query heads' rows.
-// One warp: lane -> q head g = lane / 8 and dims (lane % 8) * 4 + 32 * i, i < 4.
+// Merges the partials of pair (di, kvh) left by segments b0..b1 and writes the 4 query heads' rows.
+// One warp: lane -> q head g = lane / 8 and dims (lane % 8) * 4 + 32 * i, i < 4. The partials are
+// fetched four segments at a time, all loads of a batch in flight together: a sequence cut over many
+// segments would otherwise pay one L2 round trip per segment.
 __device__ __forceinline__ void merge_pair(const DecodeParams& P, int di, int kvh, int b0, int b1, int flat,
                                            int lane) {
-  const int g = lane >> 3, dbase = (lane & 7) * 4;
+  const int g = lane >> 3, sub8 = lane & 7, dbase = sub8 * 4;
+  const long long stride = static_cast<long long>(P.n_kv) * kGroup;  // slots from one segment to the next
+  const long long slot_b0 = ((static_cast<long long>(di) + b0) * P.n_kv + kvh) * kGroup + g;
+  const int n = b1 - b0 + 1;
   float gm = kNegBig;
-  for (int b = b0; b <= b1; ++b)
-    gm = fmaxf(gm, __ldcg(P.pm + ((static_cast<long long>(di) + b) * P.n_kv + kvh) * kGroup + g));
+  for (int i = sub8; i < n; i += 8) gm = fmaxf(gm, __ldcg(P.pm + slot_b0 + i * stride));
+  gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 1));
+  gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 2));
+  gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 4));
   float gl = 0.f;
   float4 acc[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int b = b0; b <= b1; ++b) {
-    const long long slot = ((static_cast<long long>(di) + b) * P.n_kv + kvh) * kGroup + g;
-    const float c = fast_exp2(__ldcg(P.pm + slot) - gm);
-    gl += __ldcg(P.pl + slot) * c;
+  for (int i0 = 0; i0 < n; i0 += 4) {
+    float pm4[4], pl4[4];
+    float4 v[4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(P.pa + slot * kHd + dbase + 32 * i));
-      acc[i].x += v.x * c; acc[i].y += v.y * c; acc[i].z += v.z * c; acc[i].w += v.w * c;
+    for (int u = 0; u < 4; ++u) {
+      const long long slot = slot_b0 + min(i0 + u, n - 1) * stride;  // past the end: reload the last one, weight 0
+      pm4[u] = __ldcg(P.pm + slot);
+      pl4[u] = __ldcg(P.pl + slot);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[u][i] = __ldcg(reinterpret_cast<const float4*>(P.pa + slot * kHd + dbase + 32 * i));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float c = i0 + u < n ? fast_exp2(pm4[u] - gm) : 0.f;
+      gl += pl4[u] * c;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i].x += v[u][i].x * c; acc[i].y += v[u][i].y * c; acc[i].z += v[u][i].z * c; acc[i].w += v[u][i].w * c;
+      }
     }
   }
   const float inv = gl > 0.f ? 1.f / gl : 0.f;
@@ -194,7 +228,8 @@ decode_plan_kernel(const int* __restrict__ pos, const int* __restrict__ qstart, 
     reinterpret_cast<int4*>(plan)[di] = make_int4(r, flat, qp, s_pages[di] + s_warp[warp]);
 }
 
-// HEADS = local kv heads (1, 2, 4 or 8); SUB = NW / HEADS warps share one head's pages.
+// HEADS = local kv heads served by the launch (1, 2, 4 or 8); the CTA's NW warps form SUB = NW / HEADS
+// groups of HEADS warps, and group `sub` of CTA b owns segment b * SUB + sub of the flat page list.
 template <int NW, int NS, int HEADS, int MINB, int MAXD>
 __global__ void __launch_bounds__(NW * 32, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
@@ -205,9 +240,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  float* s_mo = reinterpret_cast<float*>(smem + L::kMoOff);
-  float* s_mm = reinterpret_cast<float*>(smem + L::kMmOff);
-  float* s_ml = reinterpret_cast<float*>(smem + L::kMlOff);
   int* s_r = reinterpret_cast<int*>(smem + L::kROff);
   int* s_flat = reinterpret_cast<int*>(smem + L::kFlatOff);
   int* s_qpos = reinterpret_cast<int*>(smem + L::kQposOff);
@@ -252,20 +284,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     s_flat[di] = flat;
     s_qpos[di] = qp;
   }
-  // q, the cache and the scratch may be written by the kernel before this one: wait for it here,
-  // unless the caller declared the launch independent (then the wait moves to the very end, where
-  // it only keeps kernels completing in order).
-  // A sync_first launch (the one that re-enters scratch region 0) waits first and only then lets
-  // the next launch start, so every launch after it begins with all older launches complete.
-  if (!P.independent || P.sync_first) pdl_wait();
+  // kDecodeWaitFirst: q, the cache and the scratch may be written by the kernel before this one, so
+  // wait for it here. A sync_first launch (the one that re-enters scratch region 0) waits first in
+  // every mode and only then lets the next launch start, so every launch after it begins with all
+  // older launches complete.
+  bool waited = false;
+  if (P.mode == kDecodeWaitFirst || P.sync_first) {
+    pdl_wait();
+    waited = true;
+  }
   if (P.sync_first) pdl_launch_dependents();
   __syncthreads();
-  if (blockIdx.x == 0 && P.kvh_base == 0)
-    for (int di = tid; di < n_decode; di += NW * 32)
-      if (s_qpos[di] < 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
-        uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(s_flat[di]) * P.n_heads * kHd);
-        for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
-      }
   if (warp == 0 && !planned) {
     constexpr int kPer = MAXD / 32;
     int sum = 0;
@@ -290,16 +319,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     if (lane == 0) s_cum[n_decode] = total;
   }
   if (!planned) __syncthreads();  // the scan's results; a plan was complete at the barrier above
+  // From here on the warps of the CTA never meet again: each one streams its own segment.
 
   const int total_pages = s_cum[n_decode];
-  const int nb = static_cast<int>(gridDim.x);
-  const int W = max(2 * SUB, (total_pages + nb - 1) / nb);  // pages per CTA
-  const long long lo_ll = static_cast<long long>(blockIdx.x) * W;
-  if (lo_ll >= total_pages) {  // whole CTA leaves together; nothing in flight
-    if (blockIdx.x == 0) pdl_wait();
-    return;
-  }
-  const int lo = static_cast<int>(lo_ll);
+  const int nseg = static_cast<int>(gridDim.x) * SUB;
+  const int seg = static_cast<int>(blockIdx.x) * SUB + sub;
+  const int W = max(2, (total_pages + nseg - 1) / nseg);  // pages per segment
+  const long long lo_ll = static_cast<long long>(seg) * W;
+  const int lo = lo_ll < total_pages ? static_cast<int>(lo_ll) : total_pages;
   const int hi = min(total_pages, lo + W);
   unsigned long long* counters =
       reinterpret_cast<unsigned long long*>(P.pl + decode_counter_base(P.partial_slots, n_decode * P.n_kv));
@@ -311,7 +338,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   // ---- producer cursor: next page this warp will request ----
   ItemCursor pc;
   item_at(pc, lo, hi, n_decode, s_cum);
-  int p_page = pc.pb + sub;
+  int p_page = pc.pb;
   int p_blk = 0;
   int islot = 0;
   // Moves to the next item until this warp has a page in it; with `load` it also fetches that
@@ -319,7 +346,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   auto prod_settle = [&](bool load) {
     while (pc.off < hi && p_page >= pc.pe) {
       item_at(pc, pc.off + (pc.pe - pc.pb), hi, n_decode, s_cum);
-      p_page = pc.pb + sub;
+      p_page = pc.pb;
     }
     if (load && pc.off < hi)
       p_blk = __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page);
@@ -333,16 +360,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       tma_load_page(my_stage + islot * kPageBytes, &tmap, &my_bar[islot], 0, 0, kvh * 2, 0, p_blk);
     }
     islot = (islot + 1 == NS) ? 0 : islot + 1;
-    p_page += SUB;
+    p_page += 1;
     prod_settle(load_next);
   };
   // Filling the ring: the block ids of this warp's first NS pages are fetched with ONE load (lane j
   // takes the j-th page) instead of NS dependent ones.
   prod_settle(false);
   {
-    const int n_first = pc.off < hi ? min(NS, (pc.pe - p_page + SUB - 1) / SUB) : 0;
+    const int n_first = pc.off < hi ? min(NS, pc.pe - p_page) : 0;
     const int pre = lane < n_first
-                        ? __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page + lane * SUB)
+                        ? __ldg(P.bt + static_cast<long long>(s_r[pc.di]) * P.max_blocks + p_page + lane)
                         : 0;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
@@ -354,6 +381,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       }
     }
   }
+  // kDecodeWaitRows: the pages requested above hold only keys that were cached before the kernel
+  // ahead of this one began; the q / K / V rows of the step may be its product, so wait for it now.
+  if (P.mode == kDecodeWaitRows && !waited) pdl_wait();
+
+  if (blockIdx.x == 0 && P.kvh_base == 0)
+    for (int di = tid; di < n_decode; di += NW * 32)
+      if (s_qpos[di] < 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
+        uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(s_flat[di]) * P.n_heads * kHd);
+        for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+      }
 
   // ---- consumer ----
   const int g = lane >> 2, t = lane & 3;
@@ -377,7 +414,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   int cslot = 0;
   uint32_t cphase = 0;
   uint32_t qa[8][2], qn[8][2];
-  load_q(qa, cc.di);
+  if (cc.off < hi) load_q(qa, cc.di);
+  const long long plane_elems = static_cast<long long>(kTok) * P.n_kv * kHd;
 
 #pragma unroll 1
   while (cc.off < hi) {
@@ -390,21 +428,41 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m = kNegBig, l = 0.f;
     const int qpos = s_qpos[cc.di];
+    const int flat = s_flat[cc.di];
 
 #pragma unroll 1
-    for (int page = cc.pb + sub; page < cc.pe; page += SUB) {
+    for (int page = cc.pb; page < cc.pe; ++page) {
+      // fused append: this warp is the only one that streams the sequence's last page for this head
+      const bool appends = P.cache_w != nullptr && page == cc.np - 1;
+      uint4 new_row = make_uint4(0, 0, 0, 0);
+      int a_blk = 0;
+      if (appends) {  // lane -> plane = lane / 16 (K, V), 16-byte chunk lane % 16 of the head's 256-byte row
+        a_blk = __ldg(P.bt + static_cast<long long>(s_r[cc.di]) * P.max_blocks + page);
+        new_row = *reinterpret_cast<const uint4*>(P.q + static_cast<long long>(flat) * P.q_stride +
+                                                  (lane < 16 ? P.k_rel : P.v_rel) + kvh * kHd + (lane & 15) * 8);
+      }
       if (!dead && !mbar_wait_bounded(&my_bar[cslot], cphase)) {
         dead = true;
         report(FQB_ERR_TIMEOUT, kKidDecode, page);
       }
       uint8_t* st = my_stage + cslot * kPageBytes;
       const int nvalid = min(kTok, qpos - page * kTok + 1);
+      if (appends) {
+        const int slot = qpos & (kTok - 1), plane = lane >> 4;
+        if (static_cast<unsigned>(a_blk) < static_cast<unsigned>(P.num_blocks))
+          *reinterpret_cast<uint4*>(P.cache_w + (static_cast<long long>(a_blk) * FQB_PLANES + plane) * plane_elems +
+                                    static_cast<long long>(slot) * (P.n_kv * kHd) + kvh * kHd + (lane & 15) * 8) = new_row;
+        *reinterpret_cast<uint4*>(st + plane * kPlaneBytes + page_chunk_off(slot, lane & 15)) = new_row;
+      }
       if (nvalid < kTok) {
         // tail of the sequence's last page was never written: its V rows may hold anything
         if (lane < 16)
           for (int row = nvalid; row < kTok; ++row)
             *reinterpret_cast<uint4*>(st + kPlaneBytes + (lane >> 3) * kHalfBytes + row * 128 +
                                       ((lane & 7) << 4)) = make_uint4(0, 0, 0, 0);
+      }
+      if (appends || nvalid < kTok) {
+        // generic-proxy writes into a buffer the async proxy (TMA) refills later
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
       }
@@ -457,102 +515,40 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     const bool whole = cc.pb == 0 && cc.pe == cc.np;
-    const int flat = s_flat[cc.di];
-    const int b0 = s_cum[cc.di] / W, b1 = (s_cum[cc.di] + cc.np - 1) / W;  // CTAs that see this sequence
-    unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
-    const long long slot0 = ((static_cast<long long>(cc.di) + blockIdx.x) * P.n_kv + kvh) * kGroup;
-
-    if (SUB == 1) {
-      // the warp is the only one on this head: straight from registers, no block barrier
-      if (whole) {
-        if (g < kGroup) {
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          uint32_t* dst = reinterpret_cast<uint32_t*>(
-              P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
+    if (whole) {
+      // the pair lies inside this segment: straight from registers to `out`
+      if (g < kGroup) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(
+            P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) dst[j * 4 + t] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
-        }
-      } else {
-        if (g < kGroup) {
-          float* dst = P.pa + (slot0 + g) * kHd + 2 * t;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
-          if (t == 0) {
-            P.pm[slot0 + g] = m;
-            P.pl[slot0 + g] = l;
-          }
-          __threadfence();
-        }
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-          __threadfence();
-          last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
-          __threadfence();
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
-          if (lane == 0) *ctr = 0ull;
-        }
+        for (int j = 0; j < 16; ++j) dst[j * 4 + t] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
       }
     } else {
-      // SUB warps hold pieces of the same head: merge them through shared memory first
+      const int b0 = s_cum[cc.di] / W, b1 = (s_cum[cc.di] + cc.np - 1) / W;  // segments that see this sequence
+      unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
+      const long long slot0 = ((static_cast<long long>(cc.di) + seg) * P.n_kv + kvh) * kGroup;
       if (g < kGroup) {
-        float* dst = s_mo + (warp * kGroup + g) * kHd + 2 * t;
+        float* dst = P.pa + (slot0 + g) * kHd + 2 * t;
 #pragma unroll
         for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
         if (t == 0) {
-          s_mm[warp * kGroup + g] = m;
-          s_ml[warp * kGroup + g] = l;
+          P.pm[slot0 + g] = m;
+          P.pl[slot0 + g] = l;
         }
+        __threadfence();
       }
-      __syncthreads();
-      for (int idx = tid; idx < HEADS * kGroup * 32; idx += NW * 32) {
-        const int hl = idx / (kGroup * 32), hh = P.kvh_base + hl, h = (idx >> 5) & (kGroup - 1), d4 = (idx & 31) * 4;
-        float gm = kNegBig;
-#pragma unroll
-        for (int s = 0; s < SUB; ++s) gm = fmaxf(gm, s_mm[(s * HEADS + hl) * kGroup + h]);
-        float gl = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int s = 0; s < SUB; ++s) {
-          const int w = s * HEADS + hl;
-          const float c = fast_exp2(s_mm[w * kGroup + h] - gm);
-          gl += s_ml[w * kGroup + h] * c;
-          const float4 v = *reinterpret_cast<const float4*>(s_mo + (w * kGroup + h) * kHd + d4);
-          acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
-        }
-        if (whole) {
-          const float inv = gl > 0.f ? 1.f / gl : 0.f;
-          uint2 pk;
-          pk.x = pack_bf16(acc.x * inv, acc.y * inv);
-          pk.y = pack_bf16(acc.z * inv, acc.w * inv);
-          *reinterpret_cast<uint2*>(P.out + (static_cast<long long>(flat) * P.n_heads + hh * kGroup + h) * kHd +
-                                    d4) = pk;
-        } else {
-          const long long slot = ((static_cast<long long>(cc.di) + blockIdx.x) * P.n_kv + hh) * kGroup + h;
-          if ((idx & 31) == 0) {
-            P.pm[slot] = gm;
-            P.pl[slot] = gl;
-          }
-          *reinterpret_cast<float4*>(P.pa + slot * kHd + d4) = acc;
-          __threadfence();
-        }
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();
+        last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
+        __threadfence();
       }
-      __syncthreads();  // partials written (and the merge buffers free) before anyone takes a ticket
-      if (!whole && sub == 0) {
-        int last = 0;
-        if (lane == 0) {
-          __threadfence();
-          last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
-          __threadfence();
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
-          if (lane == 0) *ctr = 0ull;
-        }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
+        if (lane == 0) *ctr = 0ull;
       }
     }
     cc = nx;
@@ -562,10 +558,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       qa[ks][1] = qn[ks][1];
     }
   }
-  // A kernel never completes before the one launched ahead of it: CTA 0 stays until that one is
-  // done. Only CTA 0 -- a CTA that waits keeps its shared memory, and with every CTA waiting a
+  // A kernel never completes before the one launched ahead of it: one warp of CTA 0 stays until that
+  // one is done. Only one -- a CTA that waits keeps its shared memory, and with every CTA waiting a
   // quarter of each CTA's residency was spent idle here instead of hosting the next launch.
-  if (blockIdx.x == 0) pdl_wait();
+  if (blockIdx.x == 0 && warp == 0) pdl_wait();
 }
 
 }  // namespace fqb

@@ -129,14 +129,39 @@ int check_attn_shape(int n_heads, int n_kv, int head_dim, int block_size) {
 
 // ---- decode configurations -----------------------------------------------------------------------
 // One launch serves HEADS local kv heads (8, 4, 2 or 1; other head counts are covered by several
-// launches). With 8 or 4 heads every warp has a head to itself (no block barrier in the stream);
-// with fewer, SUB = NW / HEADS warps share a head and merge through shared memory per sequence.
+// launches). A CTA's NW warps form SUB = NW / HEADS groups, each group streams its own segment of the
+// flat page list, so a launch of `grid` CTAs cuts the list into grid * SUB segments.
 template <int NW_, int NS_, int HEADS_, int MINB_, int MAXD_>
-struct DecodeCfg { static constexpr int NW = NW_, NS = NS_, HEADS = HEADS_, MINB = MINB_, MAXD = MAXD_; };
+struct DecodeCfg {
+  static constexpr int NW = NW_, NS = NS_, HEADS = HEADS_, MINB = MINB_, MAXD = MAXD_, SUB = NW_ / HEADS_;
+};
 using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
+
+// Most segments any launch of a call makes when its n_kv local heads are covered by launches of 8
+// (default mode only), 4, 2 and 1 heads. Default mode: one CTA per SM for the 8-head shape, two for the
+// others; overlapped modes: one CTA per SM. The scratch is indexed with the call's n_kv, so the largest
+// launch decides.
+int max_segments(int n_kv, int sm_count, bool overlapped) {
+  int seg = 0, left = n_kv;
+  const int per = overlapped ? 1 : 2;
+  if (!overlapped && left >= 8) {
+    seg = sm_count * DecodeCfg8::SUB;
+    left %= 8;
+  }
+  if (left >= 4) {
+    seg = seg > sm_count * per * DecodeCfg4::SUB ? seg : sm_count * per * DecodeCfg4::SUB;
+    left %= 4;
+  }
+  if (left >= 2) {
+    seg = seg > sm_count * per * DecodeCfg2::SUB ? seg : sm_count * per * DecodeCfg2::SUB;
+    left %= 2;
+  }
+  if (left >= 1) seg = seg > sm_count * per * DecodeCfg1::SUB ? seg : sm_count * per * DecodeCfg1::SUB;
+  return seg;
+}
 
 unsigned next_epoch() {
   static std::atomic<unsigned> counter{0x5eed0000u};
@@ -160,12 +185,13 @@ constexpr bool pdl_enabled() {
 // reader's own wait) is always the finished plan. Early starts alone would not give that: a kernel that
 // begins at its predecessor's trigger sees only what was visible before the predecessor began.
 thread_local bool t_plain_next = false;
+thread_local cudaStream_t t_plain_stream = nullptr;  // the stream the plan kernel went to
 
 // Launches `kern` with or without the programmatic-serialization attribute.
 template <class... KArgs, class... Args>
 cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
                       Args... args) {
-  if (t_plain_next) {
+  if (t_plain_next && st == t_plain_stream) {  // a launch on another stream leaves the flag for the plan's stream
     pdl = false;
     t_plain_next = false;
   }
@@ -218,7 +244,7 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
   for (int base = 0; base < n_decode; base += Cfg::MAXD) {
     P.rids = rids + base;
     P.n_decode = n_decode - base < Cfg::MAXD ? n_decode - base : Cfg::MAXD;
-    const long long need = decode_slots_needed(P.n_decode, P.n_kv, grid);
+    const long long need = decode_slots_needed(P.n_decode, P.n_kv, grid * Cfg::SUB);
     if (need > P.partial_slots)
       return set_error(FQB_ERR_WORKSPACE, "decode scratch: %lld partial slots needed, %lld given", need,
                        P.partial_slots);
@@ -305,15 +331,25 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
 int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks) {
   (void)max_blocks;  // the split count follows the SM count, not the context length
   if (max_decode <= 0 || n_heads_local <= 0) return 0;
-  // One region holds the partials of (sequences + CTAs) segments plus the arrival counters of a
-  // launch of at most 512 sequences on at most 512 CTAs. Independent launches rotate through
+  // One region holds the partials of (sequences + segments) pieces plus the arrival counters of a
+  // launch of at most 512 sequences. Overlapping launches rotate through
   // regions; re-entering the first one is a sync point whose cost is shared by all regions, so
   // give as many as fit in about 128 Ki slots (64 MiB of pa), at least 16, at most 64.
-  const long long one = (decode_slots_needed(max_decode < 512 ? max_decode : 512, n_heads_local / kGroup, 512) + 3) & ~3LL;
+  const int n_kv = n_heads_local / kGroup;
+  // sized for a GPU of up to 256 SMs
+  const long long one =
+      (decode_slots_needed(max_decode < 512 ? max_decode : 512, n_kv, max_segments(n_kv, 256, false)) + 3) & ~3LL;
   long long regions = (128 * 1024) / one;
   if (regions < 16) regions = 16;
   if (regions > kMaxRegions) regions = kMaxRegions;
   return regions * one;
+}
+
+int64_t fqb_attn_decode_slots_needed(int n_decode, int n_kv) {
+  if (n_decode <= 0 || n_kv <= 0) return 0;
+  DeviceInfo di;
+  if (int rc = device_info(di)) return rc;
+  return decode_slots_needed(n_decode < 512 ? n_decode : 512, n_kv, max_segments(n_kv, di.sm_count, false));
 }
 
 int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids, int n_decode,
@@ -327,14 +363,16 @@ int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_
                                                                         plan);
   FQB_CUDA_TRY(cudaGetLastError());
   t_plain_next = true;
+  t_plain_stream = static_cast<cudaStream_t>(stream);
   return FQB_OK;
 }
 
+// cache_w != nullptr: the launch also appends the new token's K / V rows (fqb_append_attn_decode).
 static int decode_impl(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
                        int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
-                       const int32_t* plan, void* stream) {
+                       const int32_t* plan, void* cache_w, long long k_rel, long long v_rel, void* stream) {
   if (n_decode <= 0) return FQB_OK;
   if (plan && (n_decode > 256 || (reinterpret_cast<uintptr_t>(plan) & 15u)))
     return set_error(FQB_ERR_INVALID, "attn_decode: a step plan serves at most 256 sequences per call and must be 16-byte aligned");
@@ -348,6 +386,8 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   if (!aligned16(q) || !aligned16(cache) || !aligned16(out) || !aligned16(pa) || (q_stride % 8) ||
       (reinterpret_cast<uintptr_t>(pl) & 7u) || (reinterpret_cast<uintptr_t>(pm) & 3u))
     return set_error(FQB_ERR_INVALID, "attn_decode: q, cache, out, pa and q_stride must keep 16-byte alignment, pl 8");
+  if ((flags & FQB_DECODE_INDEPENDENT) && (flags & FQB_DECODE_HISTORY_STABLE))
+    return set_error(FQB_ERR_INVALID, "attn_decode: FQB_DECODE_INDEPENDENT and FQB_DECODE_HISTORY_STABLE exclude each other");
   DeviceInfo di;
   if (int rc = device_info(di)) return rc;
   CUtensorMap map;
@@ -370,14 +410,21 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   P.pl = pl;
   P.pa = pa;
   P.partial_slots = partial_slots;
-  P.independent = 0;
+  P.mode = kDecodeWaitFirst;
   P.sync_first = 0;
   P.plan = plan;
+  P.cache_w = static_cast<__nv_bfloat16*>(cache_w);
+  P.k_rel = k_rel;
+  P.v_rel = v_rel;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  // ---- independent launches: one CTA per SM per launch, two launches resident side by side ----
-  if ((flags & FQB_DECODE_INDEPENDENT) && pdl_enabled() && n_decode <= 256) {
-    const int64_t need = (decode_slots_needed(n_decode, n_kv, di.sm_count) + 3) & ~int64_t(3);
+  // ---- overlapping launches: one CTA per SM per launch, two launches resident side by side ----
+  // (FQB_DECODE_INDEPENDENT: no wait at all; FQB_DECODE_HISTORY_STABLE: the page ring is filled, then
+  // the launch waits for the kernel before it.) Both may touch the scratch while the launch before them
+  // still merges its partials, so consecutive launches rotate through regions of the scratch.
+  const unsigned overlap = flags & (FQB_DECODE_INDEPENDENT | FQB_DECODE_HISTORY_STABLE);
+  if (overlap && pdl_enabled() && n_decode <= 256) {
+    const int64_t need = (decode_slots_needed(n_decode, n_kv, max_segments(n_kv, di.sm_count, true)) + 3) & ~int64_t(3);
     int regions = static_cast<int>(partial_slots / need);
     if (regions > kMaxRegions) regions = kMaxRegions;
     if (regions >= 2) {
@@ -386,7 +433,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
       P.pl = pl + region * need;
       P.pa = pa + region * need * kHd;
       P.partial_slots = need;
-      P.independent = 1;
+      P.mode = (flags & FQB_DECODE_INDEPENDENT) ? kDecodeNoWait : kDecodeWaitRows;
       // The launch that re-enters region 0 waits for all earlier kernels before it lets the next
       // launch start (sync_first): a region is reused one full rotation later, and between any launch and
       // its region's previous user lies such a sync point, so the earlier user has always completed.
@@ -428,8 +475,11 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
                        void* stream) {
+  if (flags & FQB_DECODE_HISTORY_STABLE)
+    return set_error(FQB_ERR_INVALID, "attn_decode: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode "
+                                      "(a separate append kernel in front writes the cache this call reads)");
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
-                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, stream);
+                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, stream);
 }
 
 int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -437,9 +487,11 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
                             int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
                             int64_t partial_slots, unsigned flags, void* stream) {
   if (n_decode > 0 && !plan) return set_error(FQB_ERR_INVALID, "attn_decode_planned: null plan");
+  if (flags & FQB_DECODE_HISTORY_STABLE)
+    return set_error(FQB_ERR_INVALID, "attn_decode_planned: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode");
   // pos / qstart / decode_rids are not read when a plan is given; the plan pointer stands in for them
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, plan, plan, plan, n_decode, bt,
-                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, stream);
+                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, nullptr, 0, 0, stream);
 }
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -448,6 +500,26 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
                     float* pl, float* pa, int64_t partial_slots, void* stream) {
   return fqb_attn_decode_ex(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                             n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, 0u, stream);
+}
+
+int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,
+                           int k_off, int v_off, void* out, int head_dim, const int32_t* pos, const int32_t* qstart,
+                           const int32_t* decode_rids, const int32_t* plan, int n_decode, const int32_t* bt,
+                           int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
+                           int64_t partial_slots, unsigned flags, void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (!qkv) return set_error(FQB_ERR_INVALID, "append_attn_decode: null pointer");
+  if (!aligned16(qkv) || (src_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8) || q_off < 0 || k_off < 0 || v_off < 0)
+    return set_error(FQB_ERR_INVALID, "append_attn_decode: qkv, src_stride, q_off, k_off and v_off must keep 16-byte alignment");
+  if (!plan && (!pos || !qstart || !decode_rids))
+    return set_error(FQB_ERR_INVALID, "append_attn_decode: give pos / qstart / decode_rids or a step plan");
+  const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv) + q_off;
+  const int32_t* m0 = plan ? plan : pos;
+  const int32_t* m1 = plan ? plan : qstart;
+  const int32_t* m2 = plan ? plan : decode_rids;
+  return decode_impl(q, src_stride, cache, num_blocks, out, kv_heads_local * kGroup, kv_heads_local, head_dim, m0, m1, m2,
+                     n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, cache,
+                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, stream);
 }
 
 // ---- decode attention for callers that cannot provide scratch -------------------------------------
@@ -486,11 +558,16 @@ int fqb_attn_decode_static(const void* q, int q_stride, const void* cache, int n
                            const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks,
                            int block_size, float scale, void* stream) {
   if (n_decode <= 0) return FQB_OK;
-  if (n_decode > FQB_STATIC_MAX_DECODE || n_kv > FQB_STATIC_MAX_KV_HEADS)
+  // what the launches of this call would need, worked out before anything is launched
+  DeviceInfo di;
+  if (int rc = device_info(di)) return rc;
+  const long long need = n_kv > 0 ? decode_slots_needed(n_decode, n_kv, max_segments(n_kv, di.sm_count, false)) : 0;
+  if (n_decode > FQB_STATIC_MAX_DECODE || n_kv > FQB_STATIC_MAX_KV_HEADS || need > kStaticSlots)
     return set_error(FQB_ERR_WORKSPACE,
-                     "attn_decode_static: %d sequences x %d kv heads is beyond the built-in scratch "
-                     "(at most %d sequences, %d kv heads); use fqb_attn_decode with your own scratch",
-                     n_decode, n_kv, FQB_STATIC_MAX_DECODE, FQB_STATIC_MAX_KV_HEADS);
+                     "attn_decode_static: %d sequences x %d kv heads is beyond the built-in scratch (at most %d "
+                     "sequences; 1, 2, 4 or 8 kv heads; %lld of %lld partial slots needed on this GPU); use "
+                     "fqb_attn_decode with your own scratch",
+                     n_decode, n_kv, FQB_STATIC_MAX_DECODE, need, kStaticSlots);
   float* base = nullptr;
   if (int rc = fqb::static_scratch_address(&base)) return rc;
   // the arrival counters inside the scratch are tagged with a per-launch number, so nothing has to

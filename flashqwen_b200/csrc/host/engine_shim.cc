@@ -45,6 +45,20 @@ int fqb_engine_configure(int num_blocks, int64_t partial_slots) {
   if (num_blocks <= 0 || partial_slots < 0)
     return fqb::set_error(FQB_ERR_INVALID, "fqb_engine_configure: num_blocks %d, partial_slots %lld", num_blocks,
                           static_cast<long long>(partial_slots));
+  // The engine's scratch must at least serve one sequence on this GPU (a launch cuts the page list into
+  // a number of pieces that follows the SM count); an engine started with very few slots would otherwise
+  // learn of it only at its first decode step.
+  long long least = -1;
+  for (int n_kv = 1; n_kv <= 8; n_kv *= 2) {
+    const long long need = fqb_attn_decode_slots_needed(1, n_kv);
+    if (need < 0) break;  // no usable CUDA device in this process (yet): the launches will check
+    if (least < 0 || need < least) least = need;
+  }
+  if (least >= 0 && partial_slots < least)
+    return fqb::set_error(FQB_ERR_WORKSPACE,
+                          "fqb_engine_configure: %lld partial slots cannot serve a single sequence on this GPU "
+                          "(%lld needed); the engine's DecodePartialFloats(slots) gives slots*1024",
+                          static_cast<long long>(partial_slots), least);
   g_num_blocks.store(num_blocks);
   g_partial_slots.store(partial_slots);
   g_first_error.store(FQB_OK);

@@ -82,6 +82,21 @@ def attn_decode_planned(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, h
                                       _ptr(pa), partial_slots, flags, _stream(stream)), "fqb_attn_decode_planned")
 
 
+DECODE_HISTORY_STABLE = 2
+
+
+def append_attn_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos,
+                       qstart, decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa,
+                       partial_slots, stream=None, flags=0):
+    """fqb_append_attn_decode: StoreKV of the step's new token + LaunchAttnDecodeCute as one kernel
+    (engine/src/model_runtime.cu:267-273); pos / qstart / decode_rids or a step plan."""
+    check(lib.fqb_append_attn_decode(_ptr(cache), num_blocks, kv_heads_local, _ptr(qkv), src_stride, q_off, k_off,
+                                     v_off, _ptr(out), head_dim, _ptr(pos), _ptr(qstart), _ptr(decode_rids),
+                                     _ptr(plan), n_decode, _ptr(bt), max_blocks, block_size, scale, _ptr(pm),
+                                     _ptr(pl), _ptr(pa), partial_slots, flags, _stream(stream)),
+          "fqb_append_attn_decode")
+
+
 def attn_decode_static(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                        n_decode, bt, max_blocks, block_size, scale, stream=None):
     """fqb_attn_decode_static: decode attention with the library's built-in scratch, for callers that

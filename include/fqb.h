@@ -102,6 +102,9 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
  * num_blocks bounds the block ids (ids outside [0,num_blocks) read zeros and raise
  * FQB_ERR_INDEX in the device status). n_decode <= 0 is a no-op. */
 int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max_blocks);
+/* The exact number of partial slots fqb_attn_decode (flags = 0) needs for n_decode sequences and n_kv
+ * local kv heads on the CURRENT device (it follows the SM count), or a negative FQB_ERR_* code. */
+int64_t fqb_attn_decode_slots_needed(int n_decode, int n_kv);
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out,
                     int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
@@ -136,9 +139,9 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
  * reference counterpart (the reference recomputes per launch, engine/src/attn_cute.cu:172). The plan
  * is valid while pos / qstart / decode_rids are unchanged; at most FQB_PLAN_MAX_DECODE sequences to
  * build and 256 per planned call. Results are identical to fqb_attn_decode_ex. Build the plan and make
- * the step's launches from one thread: the first launch that thread makes after
- * fqb_attn_decode_plan waits for the plan in full (it is an ordinary launch), which is what makes the
- * plan visible to the prologues of all later launches. */
+ * the step's launches from ONE thread on ONE stream: the first launch that thread makes on the plan's
+ * stream after fqb_attn_decode_plan waits for the plan in full (it is an ordinary launch), which is what
+ * makes the plan visible to the prologues of all later launches on that stream. */
 #define FQB_PLAN_MAX_DECODE 1024
 int fqb_attn_decode_plan(const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids,
                          int n_decode, int max_blocks, int32_t* plan, void* stream);
@@ -146,6 +149,35 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
                             int n_heads, int n_kv, int head_dim, const int32_t* plan, int n_decode,
                             const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
                             float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
+
+/* Fused pair: KV append of the step's new token + decode attention, one kernel.
+ * replaces: the call pair KvStore::StoreKV + LaunchAttnDecodeCute of a pure-decode step
+ * (engine/src/model_runtime.cu:267-273; the steps the engine replays from CUDA graphs,
+ * engine/src/model_runtime.cu:227-233). For decode sequence di (r = decode_rids[di], flat = qstart[r],
+ * p = pos[flat]) the K and V rows of the fused row qkv + flat*src_stride (local heads at element
+ * offsets k_off / v_off, as for fqb_kv_append) are written to token slot p of block
+ * bt[r*max_blocks + p/16], and the q heads at q_off attend keys 0..p including that row; out as for
+ * fqb_attn_decode. The cache afterwards is bit-identical to fqb_kv_append over the same rows. Exactly
+ * one warp per (sequence, kv head) streams the sequence's last page; that warp stores the row and puts
+ * it into the page it has just loaded, so no other kernel has to run in front. Rows of prefill requests
+ * in a mixed step still go through fqb_kv_append (appending a decode row twice is harmless).
+ * Either pos / qstart / decode_rids or a step plan (fqb_attn_decode_plan; then the three may be NULL).
+ * The block that receives the row must be private to the sequence (fqb_cow_prepare first).
+ * flags: 0, FQB_DECODE_INDEPENDENT, or
+ *   FQB_DECODE_HISTORY_STABLE  the caller states that the kernel launched immediately before this call
+ *       writes none of the CACHED keys this call reads (positions < p of the decode sequences) and none
+ *       of the metadata; it may well produce the qkv rows. The launch then requests its first pages
+ *       while that kernel still runs and waits for it only before it reads the rows -- the dependency
+ *       the engine's layer loop really has (the kernel in front is the QKV projection or the q/k norm,
+ *       engine/src/model_runtime.cu:259-265; the layer's cache was last written one step earlier).
+ *       Scratch regions rotate as for FQB_DECODE_INDEPENDENT. Not valid directly after a kernel that
+ *       writes this cache (fqb_copy_blocks, fqb_kv_append, fqb_scatter_blocks): use flags = 0 there. */
+#define FQB_DECODE_HISTORY_STABLE 2u
+int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                           int q_off, int k_off, int v_off, void* out, int head_dim, const int32_t* pos,
+                           const int32_t* qstart, const int32_t* decode_rids, const int32_t* plan, int n_decode,
+                           const int32_t* bt, int max_blocks, int block_size, float scale, float* pm, float* pl,
+                           float* pa, int64_t partial_slots, unsigned flags, void* stream);
 
 /* Decode attention without caller scratch. No counterpart in the reference (its call site always
  * passes pm / pl / pa): this entry point exists for callers that have no device memory to give and
@@ -156,9 +188,11 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
  * fqb_attn_decode with the split-K scratch taken from a fixed 4.06 MiB array inside the library's
  * own device image (resident on every GPU that loads the library until the process exits), and it
  * calls no allocating routine of any kind.
- *   Limits: n_decode <= FQB_STATIC_MAX_DECODE and n_kv <= FQB_STATIC_MAX_KV_HEADS; beyond them the
- *   call returns FQB_ERR_WORKSPACE and launches nothing (so does the full 64 x 8 case on a GPU with
- *   more than 159 SMs, where it no longer fits the array; B200 has 148).
+ *   Limits: n_decode <= FQB_STATIC_MAX_DECODE and n_kv one of 1, 2, 4, 8 (<= FQB_STATIC_MAX_KV_HEADS).
+ *   Any other head count (3, 5, 6, 7) goes out as several launches whose partials do not fit the
+ *   array; so does the full 64 x 8 case on a GPU with more than 159 SMs (B200 has 148). What does not
+ *   fit is worked out before anything is launched: the call returns FQB_ERR_WORKSPACE, names the
+ *   limit in fqb_last_error() and launches nothing.
  *   First call on each device: looks up the array's device address (cudaGetSymbolAddress, with that
  *   device current). Make that first call outside any stream capture; later calls may be captured
  *   like the other operators.

@@ -84,7 +84,7 @@ def test_engine_launchers_refuse_to_run_before_configure():
         _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 128, 1, 1, 1, 0, 1, 8, 16, 0.1, 1, 1, 1, None)
         assert _lib.lib.fqb_engine_status() == -8
         assert b"fqb_engine_configure" in _lib.lib.fqb_engine_error()
-    assert _lib.lib.fqb_engine_configure(64, 4096) == 0
+    assert _lib.lib.fqb_engine_configure(64, 16 * 64 * 16) == 0
     assert _lib.lib.fqb_engine_status() == 0
     _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 128, 1, 1, 1, 0, 1, 8, 16, 0.1, 1, 1, 1, None)
     assert _lib.lib.fqb_engine_status() == 0

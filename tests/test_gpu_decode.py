@@ -270,3 +270,126 @@ def test_step_plan_gives_identical_results(flags, n_kv):
 def test_head_counts_that_need_several_launches(n_kv):
     c = synth.decode_case([300, 48, 1025, 7], 128, seed=500 + n_kv, n_kv=n_kv)
     assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
+
+
+# ---- fqb_append_attn_decode: the new token's KV append fused into the decode kernel ----
+def _fused_case(lengths, num_blocks, seed, n_kv, shuffle=True):
+    """A decode case whose cache does NOT hold the step's token yet: its slot is poisoned, the fused call
+    must write it from the qkv row. Returns (case, cache before the call, cache the oracle's append gives)."""
+    c = synth.decode_case(lengths, num_blocks, seed=seed, n_kv=n_kv, shuffle_rids=shuffle)
+    before = c.cache.copy()
+    for s, L in enumerate(lengths):
+        before[c.tables[s][(L - 1) // 16], :, (L - 1) % 16] = 0x7FC0
+    after = before.copy()
+    q_dim = c.n_heads * 128
+    O.kv_append(after, c.qkv, c.q_stride, q_dim, q_dim + c.n_kv * 128, c.bt, c.req, c.pos)
+    return c, before, after
+
+
+def _fused_call(c, cache, qkv, out, s, flags=0, plan=None, meta=None):
+    pos, qstart, rids, bt = meta
+    q_dim = c.n_heads * 128
+    fq.append_attn_decode(cache, c.num_blocks, c.n_kv, qkv, c.q_stride, 0, q_dim, q_dim + c.n_kv * 128, out, 128,
+                          None if plan is not None else pos, None if plan is not None else qstart,
+                          None if plan is not None else rids, plan, len(c.decode_rids), bt, c.max_blocks, 16, c.scale,
+                          s.pm, s.pl, s.pa, s.slots, flags=flags)
+
+
+@pytest.mark.parametrize("flags", [0, 1, 2])
+@pytest.mark.parametrize("n_kv", [8, 4, 2, 1])
+def test_fused_append_writes_the_cache_bit_exactly_and_attends_the_new_token(flags, n_kv):
+    lengths = [1, 15, 16, 17, 33, 100, 257, 640, 5, 1024, 2, 3000]
+    c, before, after = _fused_case(lengths, 360, seed=600 + n_kv, n_kv=n_kv)
+    cache, qkv = dv(before), dv(c.qkv)
+    meta = (dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt))
+    out = torch.full((len(lengths), c.n_heads * 128), 0x7FC0, dtype=torch.int16, device=DEV)
+    s = Scratch(len(lengths), c.n_heads, c.max_blocks)
+    for _ in range(3):   # repeated calls: the append is idempotent, the scratch regions rotate
+        _fused_call(c, cache, qkv, out, s, flags=flags, meta=meta)
+    torch.cuda.synchronize()
+    fq.device_status()
+    assert np.array_equal(host(cache), after), "cache differs from fqb_kv_append's result"
+    c.cache = after
+    assert maxabs(host(out), oracle_decode(c)) <= TOL
+
+
+def test_fused_append_with_a_step_plan_and_head_counts_that_need_several_launches():
+    lengths = [700, 33, 1500, 16, 250, 48]
+    for n_kv in (3, 8):
+        c, before, after = _fused_case(lengths, 200, seed=620 + n_kv, n_kv=n_kv)
+        cache, qkv = dv(before), dv(c.qkv)
+        meta = (dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt))
+        n = len(lengths)
+        plan = torch.zeros(4 * n + 4, dtype=torch.int32, device=DEV)
+        fq.attn_decode_plan(meta[0], meta[1], meta[2], n, c.max_blocks, plan)
+        out = torch.full((n, c.n_heads * 128), 0x7FC0, dtype=torch.int16, device=DEV)
+        s = Scratch(n, c.n_heads, c.max_blocks)
+        _fused_call(c, cache, qkv, out, s, flags=2, plan=plan, meta=meta)
+        torch.cuda.synchronize()
+        fq.device_status()
+        assert np.array_equal(host(cache), after)
+        c.cache = after
+        assert maxabs(host(out), oracle_decode(c)) <= TOL
+
+
+@pytest.mark.parametrize("flags", [1, 2])
+def test_fused_layer_loop_without_host_sync(flags):
+    """36 fused calls in a row on one stream over 3 different pools, as a layer loop issues them,
+    sharing one scratch: the launches overlap and rotate through its regions."""
+    layers = 36
+    built = [_fused_case([700, 33, 1500, 16, 250, 4000], 520, seed=640 + i, n_kv=8) for i in range(3)]
+    caches = [dv(b[1]) for b in built]
+    qkvs = [dv(b[0].qkv) for b in built]
+    metas = [(dv(b[0].pos), dv(b[0].qstart), dv(b[0].decode_rids), dv(b[0].bt)) for b in built]
+    outs = [torch.full((6, 32 * 128), 0x7FC0, dtype=torch.int16, device=DEV) for _ in range(layers)]
+    s = Scratch(6, 32, built[0][0].max_blocks)
+    for layer in range(layers):
+        k = layer % 3
+        _fused_call(built[k][0], caches[k], qkvs[k], outs[layer], s, flags=flags, meta=metas[k])
+    torch.cuda.synchronize()
+    fq.device_status()
+    for k in range(3):
+        assert np.array_equal(host(caches[k]), built[k][2])
+        built[k][0].cache = built[k][2]
+    want = [oracle_decode(b[0]) for b in built]
+    for layer in range(layers):
+        assert maxabs(host(outs[layer]), want[layer % 3]) <= TOL, layer
+
+
+def test_fused_step_in_a_cuda_graph_replays_after_the_sequences_grew():
+    """A captured pure-decode step (the engine's graph-replayed case, engine/src/model_runtime.cu:227-233):
+    replayed after every sequence has grown by one token and new rows arrived."""
+    lengths = [100, 900, 17, 3000, 16]
+    c, before, _ = _fused_case(lengths, 300, seed=660, n_kv=8, shuffle=False)
+    cache, qkv = dv(before), dv(c.qkv)
+    pos, qstart, rids, bt = dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt)
+    out = torch.zeros((5, 32 * 128), dtype=torch.int16, device=DEV)
+    s = Scratch(5, 32, c.max_blocks)
+    mirror = before.copy()
+    q_dim = 4096
+
+    def step():
+        _fused_call(c, cache, qkv, out, s, flags=2, meta=(pos, qstart, rids, bt))
+
+    step()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    rng = np.random.default_rng(661)
+    free = [b for b in range(c.num_blocks) if b not in set(np.concatenate(c.tables).tolist())]
+    for it in range(3):
+        g.replay()
+        torch.cuda.synchronize()
+        fq.device_status()
+        O.kv_append(mirror, c.qkv, c.q_stride, q_dim, q_dim + 1024, c.bt, c.req, c.pos)
+        assert np.array_equal(host(cache), mirror), it
+        c.cache = mirror
+        assert maxabs(host(out), oracle_decode(c)) <= TOL, it
+        # next step: every sequence one token longer (a new page where the last one is full), new rows
+        for sq in range(5):
+            c.pos[sq] += 1
+            if c.pos[sq] % 16 == 0:
+                c.bt[sq, c.pos[sq] // 16] = free.pop()
+        c.qkv = synth.f32_to_bf16(rng.standard_normal(c.qkv.shape, dtype=np.float32))
+        pos.copy_(dv(c.pos)); bt.copy_(dv(c.bt)); qkv.copy_(dv(c.qkv))

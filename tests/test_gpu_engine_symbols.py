@@ -40,6 +40,36 @@ def test_decode_launcher_with_the_engines_arguments_and_scratch():
     assert maxabs(host(out), GOLD["decode_config1_out"]) <= TOL
 
 
+def test_decode_launcher_with_a_full_default_batch_of_16_sequences():
+    """The engine's defaults: 16 slots (engine/src/args.h:14), so at most 16 decode sequences per step and
+    DecodePartialFloats(16) = 16 384 floats of scratch (engine/src/kernels.cuh:33-37)."""
+    fq.device_status_reset()
+    from flashqwen_b200 import synth
+    c = synth.decode_case([4000, 3000, 17, 2500, 1, 640, 33, 4096] * 2, 2400, seed=77, n_kv=8, shuffle_rids=True)
+    assert _lib.lib.fqb_engine_configure(c.num_blocks, REF_SLOTS) == 0
+    qkv, cache, pos, qstart, rids, bt = (dv(x) for x in (c.qkv, c.cache, c.pos, c.qstart, c.decode_rids, c.bt))
+    out = torch.full((16, c.n_heads * 128), 0x7FC0, dtype=torch.int16, device=DEV)
+    pm = torch.empty(REF_SLOTS, dtype=torch.float32, device=DEV)
+    pl = torch.empty(REF_SLOTS, dtype=torch.float32, device=DEV)
+    pa = torch.empty(REF_SLOTS * 128, dtype=torch.float32, device=DEV)
+    _lib.engine_symbol("LaunchAttnDecodeCute")(p(qkv), c.q_stride, p(cache), p(out), c.n_heads, c.n_kv, 128, p(pos),
+                                               p(qstart), p(rids), 16, p(bt), c.max_blocks, 16, c.scale, p(pm), p(pl),
+                                               p(pa), None)
+    torch.cuda.synchronize()
+    assert _lib.lib.fqb_engine_status() == 0, _lib.lib.fqb_engine_error()
+    fq.device_status()
+    want = O.attn_decode(c.qkv, c.q_stride, c.cache, c.n_heads, c.n_kv, c.pos, c.qstart, c.decode_rids, c.bt, c.scale,
+                         rows=16)
+    assert maxabs(host(out), want) <= TOL
+
+
+def test_configure_refuses_a_scratch_that_cannot_serve_one_sequence():
+    # slots = 4 in the engine would give 4 096 floats: below what one launch over all SMs needs
+    assert _lib.lib.fqb_engine_configure(100, 4 * 64 * 16) == -4
+    assert b"partial" in _lib.lib.fqb_last_error()
+    assert _lib.lib.fqb_engine_configure(100, REF_SLOTS) == 0
+
+
 def test_prefill_launcher_with_the_engines_arguments():
     fq.device_status_reset()
     c = cases.prefill_small()
