@@ -1,18 +1,27 @@
 #!/usr/bin/env python
 """Paged decode attention benchmark (Qwen3-8B attention shapes) for libfqb on B200.
 
-One step = one decode step of the attention path over all layers: for each of the 36 layers,
-paged GQA decode attention of a batch of 64 sequences whose context lengths are uniform in
-[1, 4096] (pages of 16 tokens, random physical block assignment from a pool sized for 64 x 4096
-tokens). Every layer has its own KV pool, so each layer's pass is HBM-cold.
+One step = one decode step of the attention path over all layers: for each of the 36 layers, the new
+token's KV append and paged GQA decode attention of a batch of 64 sequences whose context lengths
+are uniform in [1, 4096] (pages of 16 tokens, random physical block assignment from a pool sized for
+64 x 4096 tokens). Every layer has its own KV pool, so each layer's pass is HBM-cold.
 
-  value    whole-job KV bytes attended per second with everything resident in HBM (CUDA events);
+  value    whole-job KV bytes attended per second with everything resident in HBM (CUDA events), for
+           the call an engine's layer loop can make: fqb_append_attn_decode with
+           FQB_DECODE_HISTORY_STABLE (append + attention in one kernel; a launch requests its first
+           pages while the kernel before it still runs and waits for it before it reads the step's
+           rows). `modes` gives the same step in the other launch modes: `independent` (attention
+           only, launches that wait for nothing: the upper bound) and `dependent` (attention only,
+           every launch waits for the one before it), each with its roofline fraction;
   e2e      the same step driven through the C ABI from HOST buffers: the step's fused qkv rows and
-           metadata are copied in from pinned memory, each layer appends the new token's K/V and
-           runs decode attention, (N > 1: per-head outputs are all-gathered over NCCL,) and the
-           attention output is copied back -- all inside the timed region;
+           metadata are copied in from pinned memory, every layer runs the fused append + attention,
+           (N > 1: the heads are reassembled on every GPU,) and the attention output is copied back --
+           all inside the timed region;
   roofline algorithmic bytes of one layer's launch / its measured duration, against measured HBM peak;
-  cpu_baseline the scalar host oracle timed on this box's cores on a bounded sample (reported only).
+  cpu_baseline the scalar host oracle timed on this box's cores on a bounded sample (reported only);
+  secondary    (1 GPU) the other configurations, each with its own roofline fraction and clocks:
+           long-context decode (batch 8 x 32768), KV append + chunked prefill (4 x 512 rows over
+           histories 0/1024/3000/7000), and 256 x 36 prefix-block copies.
 
 With N GPUs the 8 KV heads are split N ways (no collective inside attention): total work is fixed,
 so scaling is "strong". `--impl reference` times the FlashQwen engine's own kernels (rebuilt for
@@ -39,9 +48,20 @@ Q_DIM, KV_DIM = N_HEADS * HD, N_KV * HD
 QKV_DIM = Q_DIM + 2 * KV_DIM
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch from the ncu
-# capture summarised under profiles/ (bytes per launch at the workload's full size), or None.
-NCU_TRAFFIC_BYTES = {"cfg2": 556_570_368}
+
+
+def ncu_traffic_bytes(key):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch at the workload's full
+    per-launch size, read from the ncu summary under profiles/ (its `traffic_bytes_per_launch:` line), or
+    None when the summary is missing."""
+    path = os.path.join(ROOT, "profiles", f"decode_kernel_{key}_ncu.md")
+    try:
+        for line in open(path):
+            if line.startswith("traffic_bytes_per_launch:"):
+                return int(line.split(":")[1].split()[0].replace(",", "").replace("_", ""))
+    except OSError:
+        pass
+    return None
 
 
 def parse():
@@ -60,9 +80,10 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="issue the resident step launch by launch instead of replaying a CUDA graph")
-    ap.add_argument("--dependent", dest="independent", action="store_false",
-                    help="resident loop without FQB_DECODE_INDEPENDENT: every launch waits for the one before it")
-    ap.add_argument("--skip-dependent", action="store_true", help="do not also time the dependent-launch variant")
+    ap.add_argument("--mode", default="fused", choices=["fused", "independent", "dependent"],
+                    help="which launch mode the headline value is taken in (all three are reported under `modes`)")
+    ap.add_argument("--only-mode", action="store_true", help="time the headline mode only")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (cfg4, cfg3, block copies)")
     ap.add_argument("--workload", default="decode", choices=["decode", "cfg3", "copy"],
                     help="decode: the headline step. cfg3: KV append + chunked prefill (4 x 512-row chunks over "
                          "histories 0/1024/3000/7000). copy: prefix-block copy-on-write copies over 36 layers")
@@ -202,75 +223,113 @@ class Workload:
 
 
 
-def fqb_runner(w):
-    import flashqwen_b200 as fq
+INDEPENDENT, HISTORY_STABLE = 1, 2   # FQB_DECODE_INDEPENDENT, FQB_DECODE_HISTORY_STABLE
 
-    slots = fq.decode_partial_slots(w.batch, w.hl, w.max_blocks)
-    pm = torch.empty(slots, device=w.dev)
-    pl = torch.empty(slots, device=w.dev)
-    pa = torch.empty(slots * HD, device=w.dev)
-    launches = {"n": 0}
-    fq.device_status_reset()
 
-    plan = torch.empty(4 * w.batch + 4, dtype=torch.int32, device=w.dev)
-    use_plan = w.batch <= 256
+class FqbRunner:
+    """The product's operators on one workload, counting the kernels they launch."""
 
-    def make_plan(pos, qstart, rids):
-        """Once per step: the decode metadata resolved for all layers (fqb_attn_decode_plan)."""
-        if use_plan:
-            fq.attn_decode_plan(pos, qstart, rids, w.batch, w.max_blocks, plan)
-            launches["n"] += 1
+    def __init__(self, w):
+        import flashqwen_b200 as fq
 
-    def decode(layer, qkv, bt, pos, qstart, rids, stream=None, flags=0):
-        if use_plan:
-            fq.attn_decode_planned(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD,
-                                   plan, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
-        else:
-            fq.attn_decode(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, w.out[layer], w.hl, w.kvl, HD, pos,
-                           qstart, rids, w.batch, bt, w.max_blocks, PAGE, w.scale, pm, pl, pa, slots, stream, flags)
+        self.fq, self.w = fq, w
+        self.slots = fq.decode_partial_slots(w.batch, w.hl, w.max_blocks)
+        self.pm = torch.empty(self.slots, device=w.dev)
+        self.pl = torch.empty(self.slots, device=w.dev)
+        self.pa = torch.empty(self.slots * HD, device=w.dev)
+        self.launches = 0
+        self.plan = torch.empty(4 * w.batch + 4, dtype=torch.int32, device=w.dev)
+        self.use_plan = w.batch <= 256
+        fq.device_status_reset()
+
+    def _count_decode(self, flags):
+        w = self.w
         if flags and w.batch <= 256:
-            launches["n"] += 2 if w.kvl == 8 else 1  # 8 heads go as two launches of 4
+            self.launches += 2 if w.kvl == 8 else 1   # overlapping launches: 8 heads go as two launches of 4
         else:
-            per = 512 if w.kvl == 8 else 256  # sequences one decode_kernel launch takes
-            launches["n"] += (w.batch + per - 1) // per
+            per = 512 if w.kvl == 8 else 256          # sequences one decode_kernel launch takes
+            self.launches += (w.batch + per - 1) // per
 
-    def append(layer, qkv, bt, req, pos, stream=None):
-        fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, w.k_off, w.v_off, bt, w.max_blocks,
-                     req, pos, w.batch, stream)
-        launches["n"] += 1
+    def make_plan(self, pos, qstart, rids):
+        """Once per step: the decode metadata resolved for all layers (fqb_attn_decode_plan)."""
+        if self.use_plan:
+            self.fq.attn_decode_plan(pos, qstart, rids, self.w.batch, self.w.max_blocks, self.plan)
+            self.launches += 1
 
-    def check():
-        fq.device_status()
+    def decode(self, layer, qkv, bt, pos, qstart, rids, flags=0, out=None):
+        w, fq = self.w, self.fq
+        out = w.out[layer] if out is None else out
+        if self.use_plan:
+            fq.attn_decode_planned(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, out, w.hl, w.kvl, HD,
+                                   self.plan, w.batch, bt, w.max_blocks, PAGE, w.scale, self.pm, self.pl, self.pa,
+                                   self.slots, None, flags)
+        else:
+            fq.attn_decode(qkv[layer], w.row_dim, w.pools[layer], w.num_blocks, out, w.hl, w.kvl, HD, pos, qstart, rids,
+                           w.batch, bt, w.max_blocks, PAGE, w.scale, self.pm, self.pl, self.pa, self.slots, None, flags)
+        self._count_decode(flags)
 
-    return decode, append, launches, check, make_plan
+    def fused(self, layer, qkv, bt, req, pos, qstart, rids, flags=HISTORY_STABLE, out=None):
+        """fqb_append_attn_decode: the new token's K/V rows go into the pool inside the attention kernel."""
+        w = self.w
+        out = w.out[layer] if out is None else out
+        self.fq.append_attn_decode(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, 0, w.k_off, w.v_off, out,
+                                   HD, pos, qstart, rids, self.plan if self.use_plan else None, w.batch, bt, w.max_blocks,
+                                   PAGE, w.scale, self.pm, self.pl, self.pa, self.slots, None, flags)
+        self._count_decode(flags)
+
+    def append(self, layer, qkv, bt, req, pos):
+        w = self.w
+        self.fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, w.k_off, w.v_off, bt, w.max_blocks,
+                          req, pos, w.batch)
+        self.launches += 1
+
+    def check(self):
+        self.fq.device_status()
 
 
-def ref_runner(w):
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import oracle_lib
+class RefRunner:
+    """The reference engine's own kernels (oracle/_ref/libfq_ref_cuda.so) behind the same methods."""
 
-    ref = oracle_lib.ref_cuda()
-    slots = w.batch * ref.ref_decode_max_heads() * ref.ref_decode_max_ksplit()
-    pm = torch.empty(slots, device=w.dev)
-    pl = torch.empty(slots, device=w.dev)
-    pa = torch.empty(slots * HD, device=w.dev)
-    launches = {"n": 0}
+    def __init__(self, w):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import oracle_lib
 
-    def st(stream):
-        return C.c_void_p(torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream)
+        self.ref, self.w = oracle_lib.ref_cuda(), w
+        slots = w.batch * self.ref.ref_decode_max_heads() * self.ref.ref_decode_max_ksplit()
+        self.pm = torch.empty(slots, device=w.dev)
+        self.pl = torch.empty(slots, device=w.dev)
+        self.pa = torch.empty(slots * HD, device=w.dev)
+        self.launches = 0
 
-    def decode(layer, qkv, bt, pos, qstart, rids, stream=None):
-        ref.ref_attn_decode(qkv[layer].data_ptr(), QKV_DIM, w.pools[layer].data_ptr(), w.out[layer].data_ptr(), N_HEADS,
-                            N_KV, HD, pos.data_ptr(), qstart.data_ptr(), rids.data_ptr(), w.batch, bt.data_ptr(),
-                            w.max_blocks, PAGE, w.scale, pm.data_ptr(), pl.data_ptr(), pa.data_ptr(), st(stream))
-        launches["n"] += 2
+    @staticmethod
+    def _st():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
-    def append(layer, qkv, bt, req, pos, stream=None):
-        ref.ref_store_kv(w.pools[layer].data_ptr(), N_HEADS, N_KV, HD, qkv[layer].data_ptr(), bt.data_ptr(),
-                         w.max_blocks, req.data_ptr(), pos.data_ptr(), w.batch, st(stream))
-        launches["n"] += 1
+    def make_plan(self, pos, qstart, rids):
+        pass
 
-    return decode, append, launches, lambda: None, lambda pos, qstart, rids: None
+    def decode(self, layer, qkv, bt, pos, qstart, rids, flags=0, out=None):
+        w = self.w
+        out = w.out[layer] if out is None else out
+        self.ref.ref_attn_decode(qkv[layer].data_ptr(), QKV_DIM, w.pools[layer].data_ptr(), out.data_ptr(), N_HEADS, N_KV,
+                                 HD, pos.data_ptr(), qstart.data_ptr(), rids.data_ptr(), w.batch, bt.data_ptr(),
+                                 w.max_blocks, PAGE, w.scale, self.pm.data_ptr(), self.pl.data_ptr(), self.pa.data_ptr(),
+                                 self._st())
+        self.launches += 2
+
+    def append(self, layer, qkv, bt, req, pos):
+        w = self.w
+        self.ref.ref_store_kv(w.pools[layer].data_ptr(), N_HEADS, N_KV, HD, qkv[layer].data_ptr(), bt.data_ptr(),
+                              w.max_blocks, req.data_ptr(), pos.data_ptr(), w.batch, self._st())
+        self.launches += 1
+
+    def fused(self, layer, qkv, bt, req, pos, qstart, rids, flags=0, out=None):
+        """The reference has no fused form: its own pair of calls (engine/src/model_runtime.cu:267-273)."""
+        self.append(layer, qkv, bt, req, pos)
+        self.decode(layer, qkv, bt, pos, qstart, rids, out=out)
+
+    def check(self):
+        pass
 
 
 def time_region(fn, steps, warmup, dist_on, dev):
@@ -354,7 +413,7 @@ def tensor_peak():
 def run_cfg3(a, dev):
     """Configuration 3 on one GPU: 4 sequences with 0/1024/3000/7000 cached tokens each receive a
     512-row chunk (token budget 2048): fused RMSNorm + RoPE + KV append, then causal paged attention
-    of the chunk over its full history. Prints one JSON line (secondary workload, not the headline)."""
+    of the chunk over its full history. Returns the result line as a dict (secondary workload)."""
     import flashqwen_b200 as fq
 
     hist, chunk = [0, 1024, 3000, 7000], 512
@@ -394,8 +453,7 @@ def run_cfg3(a, dev):
         import oracle_lib
         ref = oracle_lib.ref_cuda()
         if ref is None:
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libfq_ref_cuda.so not built"}))
-            return
+            return {"impl": "reference", "unavailable": "oracle/_ref/libfq_ref_cuda.so not built"}
     it = {"i": 0}
 
     def st():
@@ -425,15 +483,18 @@ def run_cfg3(a, dev):
     for i in range(nset):  # rows normalised + appended once so that the attention sees sane values
         it["i"] = i - 1
         append_step()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
     ms_app = event_ms(append_step, a.steps, a.warmup)
     ms_pre = event_ms(prefill_step, a.steps, a.warmup)
+    clocks = sampler.stop()
     if not reference:
         fq.device_status()
     flops = float(sum(N_HEADS * 4 * HD * (p + 1) for p in pos.tolist()))
     peak, src = tensor_peak()
     tf = flops / (ms_pre * 1e-3) / 1e12
     app_bytes = rows * (2 * (Q_DIM + KV_DIM) * 2 + KV_DIM * 2 + 2 * KV_DIM * 2)  # q,k read+written, v read, k,v stored
-    print(json.dumps({
+    return ({
         "metric": "chunked_prefill_attn_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_pre, 4), "higher_is_better": True,
         "dtype": "bf16", "data": "synthetic", "impl": a.impl,
@@ -441,14 +502,15 @@ def run_cfg3(a, dev):
                    "flops": flops, "l2": f"{nset} rotating pools and row sets"},
         "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(tf / peak, 4), "traffic": None, "peak_source": src},
+        "clocks": clocks,
         "append": {"kernel": "norm_rope_append (RMSNorm + RoPE + KV append)" if not reference else
                    "LaunchHeadNormRope + StoreKvKernel", "ms": round(ms_app, 4),
-                   "GB/s": round(app_bytes / (ms_app * 1e-3) / 1e9, 1), "bytes": app_bytes}}))
+                   "GB/s": round(app_bytes / (ms_app * 1e-3) / 1e9, 1), "bytes": app_bytes}})
 
 
 def run_copy(a, dev):
     """Copy-on-write copies of configuration 5's variant: 256 (shared, private) page pairs copied in
-    all 36 layers by one launch."""
+    all 36 layers by one launch. Returns the result line as a dict."""
     import flashqwen_b200 as fq
 
     layers, pairs_n, num_blocks = a.layers, 256, 4096
@@ -458,18 +520,87 @@ def run_copy(a, dev):
     ids = rng.permutation(num_blocks)[:2 * pairs_n].astype(np.int32)
     pairs = torch.from_numpy(np.stack([ids[:pairs_n], ids[pairs_n:]], 1).reshape(-1).copy()).to(dev)
     fn = lambda: fq.copy_blocks_layers(ptrs, layers, num_blocks, N_KV, pairs, pairs_n)  # noqa: E731
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
     ms = event_ms(fn, a.steps, a.warmup)
+    clocks = sampler.stop()
     fq.device_status()
     nbytes = 2 * pairs_n * 65536 * layers
     peak, src = hbm_peak()
     gbs = nbytes / (ms * 1e-3) / 1e9
-    print(json.dumps({"metric": "prefix_block_copy_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
+    return ({"metric": "prefix_block_copy_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
                       "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
                       "dtype": "u8", "data": "synthetic",
                       "config": {"workload": f"{pairs_n} page pairs x {layers} layers, 64 KiB pages", "bytes": nbytes,
                                  "l2": "1.2 GB moved per launch, larger than L2"},
+                      "clocks": clocks,
                       "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
-                                   "frac": round(gbs / peak, 4), "traffic": None, "peak_source": src}}))
+                                   "frac": round(gbs / peak, 4), "traffic": None, "peak_source": src}})
+
+
+def run_cfg4(a, dev, peak, peak_src):
+    """Configuration 4 on one GPU: batch 8 at 32768 tokens each (1 GiB of KV per layer), attention only,
+    launches that wait for nothing, over 6 layers with their own pools (6 GiB, larger than L2)."""
+    b = argparse.Namespace(**vars(a))
+    b.batch, b.fixed_ctx, b.layers, b.shard_of = 8, 32768, 6, 0
+    w = Workload(b, 0, 1, dev)
+    r = FqbRunner(w)
+
+    def step():
+        r.make_plan(w.pos, w.qstart, w.rids)
+        for layer in range(b.layers):
+            r.decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=INDEPENDENT)
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms = event_ms(step, max(a.steps, 10), a.warmup)
+    clocks = sampler.stop()
+    r.check()
+    gbs = w.bytes_layer_total * b.layers / (ms * 1e-3) / 1e9
+    return {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
+            "config": {"workload": f"{w.name}, {b.layers} layers", "kv_bytes_per_layer": w.bytes_layer_total,
+                       "l2": "6 GiB of pools walked per step, larger than L2"},
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(gbs / peak, 4), "traffic": None, "peak_source": peak_src,
+                         "launch_us": round(ms * 1e3 / b.layers, 2)}}
+
+
+def gather_check(w, a, world, rank, out_layer0, dev):
+    """Outside the timed region, N > 1: rank 0 holds 4 sequences x all 32 heads of layer 0's REASSEMBLED
+    output against the oracle. The K/V pages and q rows of those sequences are collected from the ranks'
+    own device buffers (each rank has only its heads). Returns "ok" or the max-abs difference."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    dist = torch.distributed
+    order = np.argsort(w.lengths)
+    picks = sorted({0, 1, int(order[-1]), int(order[0])})
+    while len(picks) < min(4, w.batch):
+        picks.append(max(picks) + 1)
+    blocks, bt_sel = [], np.zeros((len(picks), w.max_blocks), np.int32)
+    for i, sq in enumerate(picks):
+        nb = (w.lengths[sq] + PAGE - 1) // PAGE
+        bt_sel[i, :nb] = np.arange(len(blocks), len(blocks) + nb)
+        blocks += w.h_bt[sq, :nb].tolist()
+    idx = torch.tensor(blocks, dtype=torch.long, device=dev)
+    mine = w.pools[0][idx].contiguous()                                    # [nb, 2, 16, kvl*128]
+    pages = torch.empty((world,) + tuple(mine.shape), dtype=mine.dtype, device=dev)
+    dist.all_gather_into_tensor(pages, mine)
+    rows = w.qkv[0][torch.tensor(picks, device=dev)][:, :w.hl * HD].contiguous()   # this rank's q heads
+    qs = torch.empty((world,) + tuple(rows.shape), dtype=rows.dtype, device=dev)
+    dist.all_gather_into_tensor(qs, rows)
+    if rank != 0:
+        return None
+    import oracle_lib as O
+    cache = pages.permute(1, 2, 3, 0, 4).reshape(len(blocks), 2, PAGE, KV_DIM).contiguous()
+    q = qs.permute(1, 0, 2).reshape(len(picks), Q_DIM).contiguous()
+    u16 = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    n = len(picks)
+    want = O.attn_decode(u16(q), Q_DIM, u16(cache), N_HEADS, N_KV, np.asarray([w.lengths[s] - 1 for s in picks], np.int32),
+                         np.arange(n, dtype=np.int32), np.arange(n, dtype=np.int32), bt_sel, w.scale, rows=n)
+    got = u16(out_layer0[torch.tensor(picks, device=dev)].contiguous())
+    f32 = lambda x: (x.astype(np.uint32) << 16).view(np.float32)  # noqa: E731
+    err = float(np.max(np.abs(f32(got) - f32(want))))
+    return "ok" if err <= 2e-2 and np.isfinite(f32(got)).all() else err
 
 
 def main():
@@ -480,7 +611,7 @@ def main():
         if int(os.environ.get("RANK", "0")) != 0:
             return
         torch.cuda.set_device(0)
-        (run_cfg3 if a.workload == "cfg3" else run_copy)(a, torch.device("cuda", 0))
+        print(json.dumps((run_cfg3 if a.workload == "cfg3" else run_copy)(a, torch.device("cuda", 0))))
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -510,11 +641,11 @@ def main():
 
     w = Workload(a, rank, world, dev, full_heads=reference)
     peak, peak_src = hbm_peak()
+    # the same dict in both arms: it names the workload, not how an arm runs it
     cfg = {"workload": f"{w.name}, {a.layers} layers, page 16, Qwen3-8B attention shapes (32 q / 8 kv heads, d 128)",
            "layers": a.layers, "batch": a.batch, "sum_ctx": w.sum_ctx, "kv_bytes_per_layer": w.bytes_layer_total,
-           "parallelism": f"kv-head shard x{world}" if not reference else "single GPU",
-           "l2": "inputs larger than L2: every layer has its own pool and the step walks all of them",
-           "cuda_graph": bool(a.graph), "independent_launches": bool(a.independent)}
+           "parallelism": f"8 kv heads over {a.gpus} GPU(s), no collective inside attention",
+           "l2": "inputs larger than L2: every layer has its own pool and the step walks all of them"}
 
     if reference and not ref_gpu:
         # CPU arm: the oracle port on a bounded sample per step
@@ -530,20 +661,20 @@ def main():
         print(json.dumps(line))
         return
 
-    decode, append, launches, check, make_plan = (ref_runner if reference else fqb_runner)(w)
+    r = (RefRunner if reference else FqbRunner)(w)
 
-    # ---- kernel-only: everything resident ----
-    def measure_resident(flags, use_graph):
+    # ---- kernel-only: everything resident, one CUDA graph per step ----
+    def measure_resident(mode):
         def step_resident():
-            make_plan(w.pos, w.qstart, w.rids)
+            r.make_plan(w.pos, w.qstart, w.rids)
             for layer in range(a.layers):
-                if flags:
-                    decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=flags)
+                if mode == "fused":
+                    r.fused(layer, w.qkv, w.bt, w.req, w.pos, w.qstart, w.rids, flags=HISTORY_STABLE)
                 else:
-                    decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
+                    r.decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=INDEPENDENT if mode == "independent" else 0)
 
         run_step, per_step = step_resident, None
-        if use_graph:
+        if a.graph:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -551,53 +682,78 @@ def main():
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            launches["n"] = 0
+            r.launches = 0
             with torch.cuda.graph(graph):
                 step_resident()
-            per_step = launches["n"]
+            per_step = r.launches
             run_step = graph.replay
-        launches["n"] = 0
+        r.launches = 0
         t = time_region(run_step, a.steps, a.warmup, dist_on, dev)
-        n = per_step * a.steps if use_graph else launches["n"] * a.steps // (a.steps + a.warmup)
-        return t, n
+        n = per_step * a.steps if a.graph else r.launches * a.steps // (a.steps + a.warmup)
+        r.check()
+        return t / a.steps, n
 
-    dflags = 1 if (a.independent and not reference) else 0
+    def mode_entry(ms_step):
+        layer_s = ms_step * 1e-3 / a.layers
+        ach = w.bytes_layer_rank / layer_s / 1e9
+        return {"ms_per_step": round(ms_step, 4), "value": round(w.bytes_layer_total * a.layers / (ms_step * 1e-3) / 1e9, 2),
+                "unit": "GB/s", "launch_us": round(layer_s * 1e6, 3),
+                "roofline": {"achieved": round(ach, 2), "peak": peak, "frac": round(ach / peak, 4)}}
+
+    what = {"fused": "fqb_append_attn_decode + FQB_DECODE_HISTORY_STABLE: append and attention in one kernel; a launch "
+                     "requests its first pages early and waits for the kernel before it before reading the step's rows "
+                     "(what an engine's layer loop can call)",
+            "independent": "fqb_attn_decode_planned + FQB_DECODE_INDEPENDENT: attention only, launches wait for nothing "
+                           "(upper bound; valid only over independent caches)",
+            "dependent": "fqb_attn_decode_planned, flags 0: attention only, every launch waits for the one before it"}
+    if reference:
+        what = {"fused": "StoreKvKernel + CuteDecodeSplitKernel + CuteDecodeCombineKernel per layer (the reference's own calls)",
+                "dependent": "CuteDecodeSplitKernel + CuteDecodeCombineKernel per layer (attention only)"}
+    head_mode = a.mode if a.mode in what else "fused"
     sampler = ClockSampler(local)
     sampler.start()
-    ms, n_launch = measure_resident(dflags, a.graph)
+    ms_step, n_launch = measure_resident(head_mode)
     clocks = sampler.stop()
-    check()
-    ms_step = ms / a.steps
+    modes = {head_mode: dict(mode_entry(ms_step), call=what[head_mode])}
+    if not a.only_mode:
+        for m in what:
+            if m != head_mode:
+                ms_m, _ = measure_resident(m)
+                modes[m] = dict(mode_entry(ms_m), call=what[m])
     value = w.bytes_layer_total * a.layers / (ms_step * 1e-3) / 1e9
     layer_s = ms_step * 1e-3 / a.layers
     achieved = w.bytes_layer_rank / layer_s / 1e9
-    dependent = None
-    if dflags and not a.skip_dependent:  # the same step with every launch waiting for the one before it
-        ms_d, _ = measure_resident(0, a.graph)
-        check()
-        dependent = {"ms_per_step": round(ms_d / a.steps, 4),
-                     "value": round(w.bytes_layer_total * a.layers / (ms_d / a.steps * 1e-3) / 1e9, 2), "unit": "GB/s"}
 
-    # ---- attention + all-gather of the per-head outputs (N > 1) ----
-    gather_ms = None
+    # ---- attention + reassembly of the per-head outputs on every GPU (N > 1) ----
+    gather = None
     if dist_on:
         gathered = torch.empty((world, a.batch, w.hl * HD), dtype=torch.bfloat16, device=dev)
 
         def step_gather():
-            make_plan(w.pos, w.qstart, w.rids)
+            r.make_plan(w.pos, w.qstart, w.rids)
             for layer in range(a.layers):
-                decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids)
+                r.fused(layer, w.qkv, w.bt, w.req, w.pos, w.qstart, w.rids, flags=HISTORY_STABLE)
                 torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
 
-        gather_ms = time_region(step_gather, a.steps, a.warmup, dist_on, dev) / a.steps
+        g_ms = time_region(step_gather, a.steps, a.warmup, dist_on, dev) / a.steps
+        gather = {"ms_per_step": round(g_ms, 4), "value": round(w.bytes_layer_total * a.layers / (g_ms * 1e-3) / 1e9, 2),
+                  "how": "one NCCL all-gather per layer, launched from the host after that layer's kernel"}
 
     # ---- end to end from host buffers ----
-    e2e = None
+    e2e, check = None, None
     if not a.no_e2e:
         d_qkv = torch.empty_like(w.qkv)
         d_bt, d_pos = torch.empty_like(w.bt), torch.empty_like(w.pos)
         d_qstart, d_rids, d_req = torch.empty_like(w.qstart), torch.empty_like(w.rids), torch.empty_like(w.req)
-        h2d = sum(t.numel() * t.element_size() for t in (w.h_qkv, w.h_bt, w.h_pos, w.h_qstart, w.h_rids, w.h_req))
+        # the step's metadata travels as ONE pinned buffer and one copy (the engine makes eight,
+        # engine/src/model_runtime.cu:47-108): [bt | pos | qstart | rids | req], views on both sides
+        parts = (w.h_bt.view(-1), w.h_pos, w.h_qstart, w.h_rids, w.h_req)
+        h_meta = torch.cat(parts).pin_memory()
+        d_meta = torch.empty_like(h_meta, device=dev)
+        offs = np.cumsum([0] + [p.numel() for p in parts])
+        d_bt, d_pos, d_qstart, d_rids, d_req = (d_meta[offs[i]:offs[i + 1]] for i in range(5))
+        d_bt = d_bt.view(w.h_bt.shape)
+        h2d = w.h_qkv.numel() * w.h_qkv.element_size() + h_meta.numel() * h_meta.element_size()
         d2h = w.h_out.numel() * w.h_out.element_size()
 
         copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -613,26 +769,22 @@ def main():
         gathered_all = torch.empty((world, w.out.numel()), dtype=torch.bfloat16, device=dev) if dist_on else None
 
         def step_core():
-            """Copies in, per-layer append + decode, and the chunked copy back of this rank's outputs."""
+            """Copies in, the fused append + attention per layer, and the chunked copy back of this rank's outputs."""
             main = torch.cuda.current_stream()
             copy_in.wait_stream(main)
             copy_out.wait_stream(main)
             with torch.cuda.stream(copy_in):
-                d_bt.copy_(w.h_bt, non_blocking=True)
-                d_pos.copy_(w.h_pos, non_blocking=True)
-                d_qstart.copy_(w.h_qstart, non_blocking=True)
-                d_rids.copy_(w.h_rids, non_blocking=True)
-                d_req.copy_(w.h_req, non_blocking=True)
+                d_meta.copy_(h_meta, non_blocking=True)
                 for i, (l0, l1) in enumerate(chunks):
                     d_qkv[l0:l1].copy_(w.h_qkv[l0:l1], non_blocking=True)
                     ev_in[i].record(copy_in)
             for i, (l0, l1) in enumerate(chunks):
                 main.wait_event(ev_in[i])
                 if i == 0:
-                    make_plan(d_pos, d_qstart, d_rids)
+                    r.make_plan(d_pos, d_qstart, d_rids)
                 for layer in range(l0, l1):
-                    append(layer, d_qkv, d_bt, d_req, d_pos)
-                    decode(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids)
+                    # a chunk's first launch follows a copy that wrote its rows: an event wait orders it in full
+                    r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=HISTORY_STABLE)
                 ev_out[i].record(main)
                 with torch.cuda.stream(copy_out):
                     copy_out.wait_event(ev_out[i])
@@ -663,12 +815,19 @@ def main():
             torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
         ms_e = time_region(step_e2e_sync, a.steps, a.warmup, dist_on, dev) / a.steps
-        check()
+        r.check()
         e2e = {"value": round(w.bytes_layer_total * a.layers / (ms_e * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(ms_e, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "includes": "H2D of qkv rows + metadata (chunks of up to 6 layers on a copy stream, first and last chunk one layer), per-layer KV append + decode attention"
+               "includes": "H2D of the qkv rows (chunks of up to 6 layers on a copy stream, first and last chunk one layer) "
+                           "and of the step metadata (one pinned buffer, one copy), per layer "
+                           + ("the reference's KV append + decode attention" if reference else
+                              "the fused KV append + decode attention (FQB_DECODE_HISTORY_STABLE)")
                            + (", one NCCL all-gather of all layers' head outputs" if dist_on else "") + ", D2H of the output"
                            + ("; one CUDA graph per step, host sync every step" if a.graph else "")}
+        if dist_on:
+            # the reassembled rows of layer 0 against the oracle, outside the timed region
+            lay0 = gathered_all.view(world, a.layers, a.batch, w.hl * HD)[:, 0].permute(1, 0, 2).reshape(a.batch, Q_DIM)
+            check = gather_check(w, a, world, rank, lay0, dev)
 
     if rank != 0:
         if dist_on:
@@ -678,35 +837,51 @@ def main():
     line = {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(value, 2), "unit": "GB/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "mode": {"headline": head_mode, "cuda_graph": bool(a.graph)},
             "tokens_per_s_per_layer": round(a.batch / layer_s, 1),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
-                         "traffic": NCU_TRAFFIC_BYTES.get(w.key) if (world == 1 and not reference and not a.shard_of) else None,
+                         "traffic": ncu_traffic_bytes(w.key) if (world == 1 and not reference and not a.shard_of) else None,
                          "peak_source": peak_src,
-                         "kernel": ("CuteDecodeSplitKernel + CuteDecodeCombineKernel (reference), two launches per layer"
+                         "kernel": ("StoreKvKernel + CuteDecodeSplitKernel + CuteDecodeCombineKernel (reference), three launches per layer"
                                     if reference else
-                                    "decode_kernel (split-K + fused combine), per layer, per GPU"),
+                                    "decode_kernel (KV append + split-K attention + fused combine), per layer, per GPU"),
                          "algorithmic_bytes_per_launch": w.bytes_layer_rank,
                          "launch_us": round(layer_s * 1e6, 3)},
+            "modes": modes,
             "clocks": clocks, "gpu_launches": n_launch}
-    if dependent is not None:
-        line["dependent_launches"] = dependent
-    if gather_ms is not None:
-        line["with_all_gather"] = {"ms_per_step": round(gather_ms, 4),
-                                   "value": round(w.bytes_layer_total * a.layers / (gather_ms * 1e-3) / 1e9, 2)}
+    if "dependent" in modes:
+        line["roofline_dependent"] = dict(modes["dependent"]["roofline"], bound="hbm", unit="GB/s")
+    if gather is not None:
+        line["with_all_gather"] = gather
     if e2e is not None:
         line["e2e"] = e2e
+    if check is not None:
+        line["gather_check"] = check
     if reference:
         line["impl"] = "reference"
         line["ran_on_gpus"] = 1   # the reference engine is single-GPU: rank 0 runs the whole workload at every --gpus N
         line["cpu_baseline"] = {"value": round(value, 2), "unit": "GB/s", "cores": 0, "kind": "reference",
                                 "sample": "the reference has no CPU implementation of this path: its own CUDA kernels "
                                           "(kv_store.cu, attn_cute.cu rebuilt for sm_100a) on the full workload, 1 GPU"}
-    elif not a.no_cpu_baseline and a.gpus == 1 and w.row_dim == QKV_DIM:
-        line["cpu_baseline"] = cpu_oracle_rate(w, a)
+    else:
+        if not a.no_cpu_baseline and a.gpus == 1 and w.row_dim == QKV_DIM:
+            line["cpu_baseline"] = cpu_oracle_rate(w, a)
+        if world == 1 and not a.no_secondary and not a.shard_of and not a.fixed_ctx:
+            # free the headline workload first: the other configurations bring their own pools
+            del r
+            w.pools.clear()
+            torch.cuda.empty_cache()
+            sec = argparse.Namespace(**vars(a))
+            sec.steps, sec.warmup = max(a.steps, 20), max(a.warmup, 3)
+            line["secondary"] = {"cfg4_long_context_decode": run_cfg4(sec, dev, peak, peak_src),
+                                 "cfg3_append_prefill": run_cfg3(sec, dev),
+                                 "cfg5_block_copies": run_copy(sec, dev)}
     print(json.dumps(line))
     if dist_on:
         torch.distributed.destroy_process_group()
+    if check is not None and check != "ok":
+        raise SystemExit(f"gather_check failed: max-abs {check}")
 
 
 if __name__ == "__main__":

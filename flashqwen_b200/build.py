@@ -28,6 +28,7 @@ def build(verbose=False, force=False):
            "-Xcompiler", "-fPIC", "-shared", "-o", out_path()] + [os.path.join(HERE, s) for s in SOURCES]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
+    cmd[1:1] = [x for x in sys.argv[1:] if x.startswith("-D")]  # build-time choices, e.g. -DFQB_DEFAULT_CTAS_PER_SM=1
     subprocess.run(cmd, check=True)
     return out_path()
 

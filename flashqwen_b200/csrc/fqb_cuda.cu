@@ -140,13 +140,19 @@ using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
 
+// CTAs per SM of a default-mode launch of the 4-, 2- and 1-head shapes (build-time choice).
+#ifndef FQB_DEFAULT_CTAS_PER_SM
+#define FQB_DEFAULT_CTAS_PER_SM 2
+#endif
+constexpr int kDefaultCtas = FQB_DEFAULT_CTAS_PER_SM;
+
 // Most segments any launch of a call makes when its n_kv local heads are covered by launches of 8
 // (default mode only), 4, 2 and 1 heads. Default mode: one CTA per SM for the 8-head shape, two for the
 // others; overlapped modes: one CTA per SM. The scratch is indexed with the call's n_kv, so the largest
 // launch decides.
 int max_segments(int n_kv, int sm_count, bool overlapped) {
   int seg = 0, left = n_kv;
-  const int per = overlapped ? 1 : 2;
+  const int per = overlapped ? 1 : kDefaultCtas;
   if (!overlapped && left >= 8) {
     seg = sm_count * DecodeCfg8::SUB;
     left %= 8;
@@ -461,9 +467,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     P.kvh_base = base;
     int rc, took;
     if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
-    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 4; }
-    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 2; }
-    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 2, true, st); took = 1; }
+    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
+    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
+    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
     if (rc != FQB_OK) return rc;
     base += took;
   }

@@ -93,7 +93,10 @@ def test_prefill_launcher_with_the_engines_arguments():
 
 def test_a_failed_launch_is_kept_until_configure_is_called_again():
     c = cases.decode_config1()
-    assert _lib.lib.fqb_engine_configure(c.num_blocks, 8) == 0      # scratch far too small
+    # a scratch that can serve one kv head (so configure takes it) but not this call's 8 heads x 4 sequences
+    small = _lib.lib.fqb_attn_decode_slots_needed(1, 1) + 8
+    assert small < _lib.lib.fqb_attn_decode_slots_needed(4, 8)
+    assert _lib.lib.fqb_engine_configure(c.num_blocks, small) == 0
     t = torch.zeros(64, dtype=torch.int32, device=DEV)
     _lib.engine_symbol("LaunchAttnDecodeCute")(p(t), c.q_stride, p(t), p(t), c.n_heads, c.n_kv, 128, p(t), p(t), p(t),
                                                4, p(t), c.max_blocks, 16, c.scale, p(t), p(t), p(t), None)
