@@ -6,17 +6,20 @@ token's KV append and paged GQA decode attention of a batch of 64 sequences whos
 are uniform in [1, 4096] (pages of 16 tokens, random physical block assignment from a pool sized for
 64 x 4096 tokens). Every layer has its own KV pool, so each layer's pass is HBM-cold.
 
-  value    whole-job KV bytes attended per second with everything resident in HBM (CUDA events), for
-           the call an engine's layer loop can make: fqb_append_attn_decode with
-           FQB_DECODE_HISTORY_STABLE (append + attention in one kernel; a launch requests its first
-           pages while the kernel before it still runs and waits for it before it reads the step's
-           rows). `modes` gives the same step in the other launch modes: `independent` (attention
-           only, launches that wait for nothing: the upper bound) and `dependent` (attention only,
-           every launch waits for the one before it), each with its roofline fraction;
-  e2e      the same step driven through the C ABI from HOST buffers: the step's fused qkv rows and
-           metadata are copied in from pinned memory, every layer runs the fused append + attention,
-           (N > 1: the heads are reassembled on every GPU,) and the attention output is copied back --
-           all inside the timed region;
+  value    whole-job KV bytes attended per second with everything resident in HBM (CUDA events), with
+           launches that wait for nothing (FQB_DECODE_INDEPENDENT): the 36 layers of this step are 36
+           independent problems (own pools, rows and outputs), which is what that flag is for, and it is
+           the streaming rate of the kernel. `modes` gives the same step in the other launch modes, each
+           with its roofline fraction: `dependent` (every launch waits for the one before it, what any
+           caller may use; also reported as `roofline_dependent`) and `fused` (fqb_append_attn_decode
+           with FQB_DECODE_HISTORY_STABLE: append + attention in one kernel; a launch requests its first
+           pages while the kernel before it still runs and waits for it before it reads the step's rows
+           -- the call an engine's layer loop can make);
+  e2e      the same step driven through the C ABI from HOST buffers with the engine-usable call: the
+           step's fused qkv rows and metadata are copied in from pinned memory, every layer runs the
+           fused append + attention (FQB_DECODE_HISTORY_STABLE), (N > 1: the heads are reassembled on
+           every GPU,) and the attention output is copied back -- all inside the timed region.
+           `e2e_independent` is the same loop with FQB_DECODE_INDEPENDENT;
   roofline algorithmic bytes of one layer's launch / its measured duration, against measured HBM peak;
   cpu_baseline the scalar host oracle timed on this box's cores on a bounded sample (reported only);
   secondary    (1 GPU) the other configurations, each with its own roofline fraction and clocks:
@@ -80,7 +83,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="issue the resident step launch by launch instead of replaying a CUDA graph")
-    ap.add_argument("--mode", default="fused", choices=["fused", "independent", "dependent"],
+    ap.add_argument("--mode", default="independent", choices=["fused", "independent", "dependent"],
                     help="which launch mode the headline value is taken in (all three are reported under `modes`)")
     ap.add_argument("--only-mode", action="store_true", help="time the headline mode only")
     ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (cfg4, cfg3, block copies)")
@@ -709,7 +712,7 @@ def main():
     if reference:
         what = {"fused": "StoreKvKernel + CuteDecodeSplitKernel + CuteDecodeCombineKernel per layer (the reference's own calls)",
                 "dependent": "CuteDecodeSplitKernel + CuteDecodeCombineKernel per layer (attention only)"}
-    head_mode = a.mode if a.mode in what else "fused"
+    head_mode = a.mode if a.mode in what else "dependent"   # the reference's attention-only pair of kernels
     sampler = ClockSampler(local)
     sampler.start()
     ms_step, n_launch = measure_resident(head_mode)
@@ -740,7 +743,7 @@ def main():
                   "how": "one NCCL all-gather per layer, launched from the host after that layer's kernel"}
 
     # ---- end to end from host buffers ----
-    e2e, check = None, None
+    e2e, e2e_ind, check = None, None, None
     if not a.no_e2e:
         d_qkv = torch.empty_like(w.qkv)
         d_bt, d_pos = torch.empty_like(w.bt), torch.empty_like(w.pos)
@@ -768,7 +771,7 @@ def main():
 
         gathered_all = torch.empty((world, w.out.numel()), dtype=torch.bfloat16, device=dev) if dist_on else None
 
-        def step_core():
+        def step_core(flags=HISTORY_STABLE):
             """Copies in, the fused append + attention per layer, and the chunked copy back of this rank's outputs."""
             main = torch.cuda.current_stream()
             copy_in.wait_stream(main)
@@ -784,38 +787,48 @@ def main():
                     r.make_plan(d_pos, d_qstart, d_rids)
                 for layer in range(l0, l1):
                     # a chunk's first launch follows a copy that wrote its rows: an event wait orders it in full
-                    r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=HISTORY_STABLE)
+                    r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=flags)
                 ev_out[i].record(main)
                 with torch.cuda.stream(copy_out):
                     copy_out.wait_event(ev_out[i])
                     w.h_out[l0:l1].copy_(w.out[l0:l1], non_blocking=True)
             main.wait_stream(copy_out)
 
-        core = step_core
-        if a.graph:
-            # the engine replays decode steps from CUDA graphs: copies and kernels of one step are
-            # captured once and replayed, which takes the Python launch cost out. The collective
-            # stays outside the graph.
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step_core()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            g_e2e = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_e2e):
-                step_core()
-            core = g_e2e.replay
+        def time_e2e(flags):
+            core = lambda: step_core(flags)  # noqa: E731
+            if a.graph:
+                # the engine replays decode steps from CUDA graphs: copies and kernels of one step are
+                # captured once and replayed, which takes the Python launch cost out. The collective
+                # stays outside the graph.
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step_core(flags)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                g_e2e = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_e2e):
+                    step_core(flags)
+                core = g_e2e.replay
 
-        def step_e2e_sync():
-            core()
-            if dist_on:  # per-head outputs of all layers reassembled on the GPUs by ONE all-gather (the host
-                #          has read this rank's heads chunk by chunk inside the step already)
-                torch.distributed.all_gather_into_tensor(gathered_all, w.out.view(-1))
-            torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+            def step_e2e_sync():
+                core()
+                if dist_on:  # per-head outputs of all layers reassembled on the GPUs by ONE all-gather (the host
+                    #          has read this rank's heads chunk by chunk inside the step already)
+                    torch.distributed.all_gather_into_tensor(gathered_all, w.out.view(-1))
+                torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
-        ms_e = time_region(step_e2e_sync, a.steps, a.warmup, dist_on, dev) / a.steps
-        r.check()
+            t = time_region(step_e2e_sync, a.steps, a.warmup, dist_on, dev) / a.steps
+            r.check()
+            return t
+
+        ms_e = time_e2e(HISTORY_STABLE)
+        e2e_ind = None
+        if not reference and not a.only_mode:
+            ms_i = time_e2e(INDEPENDENT)
+            e2e_ind = {"value": round(w.bytes_layer_total * a.layers / (ms_i * 1e-3) / 1e9, 2), "unit": "GB/s",
+                       "ms_per_step": round(ms_i, 4),
+                       "note": "the same loop with FQB_DECODE_INDEPENDENT (valid here: every layer has its own pool and rows)"}
         e2e = {"value": round(w.bytes_layer_total * a.layers / (ms_e * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(ms_e, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "includes": "H2D of the qkv rows (chunks of up to 6 layers on a copy stream, first and last chunk one layer) "
@@ -843,9 +856,9 @@ def main():
                          "frac": round(achieved / peak, 4),
                          "traffic": ncu_traffic_bytes(w.key) if (world == 1 and not reference and not a.shard_of) else None,
                          "peak_source": peak_src,
-                         "kernel": ("StoreKvKernel + CuteDecodeSplitKernel + CuteDecodeCombineKernel (reference), three launches per layer"
+                         "kernel": ("CuteDecodeSplitKernel + CuteDecodeCombineKernel (reference), two launches per layer"
                                     if reference else
-                                    "decode_kernel (KV append + split-K attention + fused combine), per layer, per GPU"),
+                                    "decode_kernel (split-K attention + fused combine), per layer, per GPU"),
                          "algorithmic_bytes_per_launch": w.bytes_layer_rank,
                          "launch_us": round(layer_s * 1e6, 3)},
             "modes": modes,
@@ -856,6 +869,8 @@ def main():
         line["with_all_gather"] = gather
     if e2e is not None:
         line["e2e"] = e2e
+        if e2e_ind is not None:
+            line["e2e_independent"] = e2e_ind
     if check is not None:
         line["gather_check"] = check
     if reference:

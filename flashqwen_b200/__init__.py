@@ -7,6 +7,7 @@ tests and benchmarks read like calls into that engine. There is no CPU or PyTorc
 operator raises if the library is missing.
 """
 from ._lib import FqbError, lib, library_path  # noqa: F401
+from .driver import StepDriver, rope_tables  # noqa: F401
 from .host import BlockAllocator, acquire_prefix, cache_blocks, cow_prepare, hash_block, step_pack  # noqa: F401
 from .ops import (  # noqa: F401
     DECODE_HISTORY_STABLE,

@@ -50,6 +50,13 @@ SIGNATURES = {
                                      _p]),
     "fqb_append_attn_decode": (_i, [_p, _i, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p,
                                     _i64, C.c_uint, _p]),
+    "fqb_rope_tables": (None, [_p, _p, _i, _i, _f]),
+    "fqb_driver_create": (_i, [_p, _p, _p, _p, _p, _p, _p, _p]),
+    "fqb_driver_destroy": (None, [_p]),
+    "fqb_driver_submit": (_i, [_p, _p, _i, _i]),
+    "fqb_driver_busy": (_i, [_p]),
+    "fqb_driver_step": (_i, [_p]),
+    "fqb_driver_get_stats": (_i, [_p, _p]),
     "fqb_attn_decode_static": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
     "fqb_attn_prefill": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
     "fqb_copy_blocks": (_i, [_p, _i, _i, _p, _i, _p]),

@@ -4,7 +4,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["csrc/fqb_cuda.cu", "csrc/host/errors.cc", "csrc/host/allocator.cc", "csrc/host/layout.cc", "csrc/host/engine_shim.cc"]
+SOURCES = ["csrc/fqb_cuda.cu", "csrc/host/errors.cc", "csrc/host/allocator.cc", "csrc/host/layout.cc", "csrc/host/engine_shim.cc", "csrc/host/step_driver.cc"]
 HEADERS = ["csrc/common.cuh", "csrc/decode.cuh", "csrc/umma.cuh", "csrc/prefill_tc_ks.cuh", "csrc/kv_append.cuh", "csrc/blocks.cuh",
            "csrc/errors.h", "../include/fqb.h"]
 

@@ -140,9 +140,10 @@ using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
 
-// CTAs per SM of a default-mode launch of the 4-, 2- and 1-head shapes (build-time choice).
+// CTAs per SM of a default-mode launch of the 4-, 2- and 1-head shapes (build-time choice; measured on
+// B200 with every launch waiting for the one before it: 1 beats 2 for the 4-head and the 1-head shape).
 #ifndef FQB_DEFAULT_CTAS_PER_SM
-#define FQB_DEFAULT_CTAS_PER_SM 2
+#define FQB_DEFAULT_CTAS_PER_SM 1
 #endif
 constexpr int kDefaultCtas = FQB_DEFAULT_CTAS_PER_SM;
 
@@ -311,9 +312,10 @@ int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_
                          const float* cos_tab, const float* sin_tab, float eps, const int32_t* bt,
                          int bt_stride, const int32_t* bt_row, const int32_t* pos, int M, void* stream) {
   if (M <= 0) return FQB_OK;
-  if (!cache || !qkv || !bt || !bt_row || !pos || !wq || !wk || !cos_tab || !sin_tab)
+  // cache == NULL: RMSNorm + RoPE only (LaunchHeadNormRope alone); bt / bt_row are then not read
+  if (!qkv || !pos || !wq || !wk || !cos_tab || !sin_tab || (cache && (!bt || !bt_row)))
     return set_error(FQB_ERR_INVALID, "norm_rope_append: null pointer");
-  if (num_blocks <= 0 || kv_heads_local <= 0 || q_heads_local < 0 || bt_stride <= 0)
+  if (kv_heads_local <= 0 || q_heads_local < 0 || (cache && (num_blocks <= 0 || bt_stride <= 0)))
     return set_error(FQB_ERR_INVALID, "norm_rope_append: non-positive size");
   if (!aligned16(cache) || !aligned16(qkv) || (src_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8) ||
       (reinterpret_cast<uintptr_t>(cos_tab) & 7u) || (reinterpret_cast<uintptr_t>(sin_tab) & 7u) ||
@@ -424,12 +426,10 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   P.v_rel = v_rel;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  // ---- overlapping launches: one CTA per SM per launch, two launches resident side by side ----
-  // (FQB_DECODE_INDEPENDENT: no wait at all; FQB_DECODE_HISTORY_STABLE: the page ring is filled, then
-  // the launch waits for the kernel before it.) Both may touch the scratch while the launch before them
-  // still merges its partials, so consecutive launches rotate through regions of the scratch.
-  const unsigned overlap = flags & (FQB_DECODE_INDEPENDENT | FQB_DECODE_HISTORY_STABLE);
-  if (overlap && pdl_enabled() && n_decode <= 256) {
+  // ---- launches that wait for nothing: one CTA per SM per launch, two launches resident side by side ----
+  // Such a launch may touch the scratch while the launch before it still merges its partials, so
+  // consecutive launches rotate through regions of the scratch.
+  if ((flags & FQB_DECODE_INDEPENDENT) && pdl_enabled() && n_decode <= 256) {
     const int64_t need = (decode_slots_needed(n_decode, n_kv, max_segments(n_kv, di.sm_count, true)) + 3) & ~int64_t(3);
     int regions = static_cast<int>(partial_slots / need);
     if (regions > kMaxRegions) regions = kMaxRegions;
@@ -439,7 +439,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
       P.pl = pl + region * need;
       P.pa = pa + region * need * kHd;
       P.partial_slots = need;
-      P.mode = (flags & FQB_DECODE_INDEPENDENT) ? kDecodeNoWait : kDecodeWaitRows;
+      P.mode = kDecodeNoWait;
       // The launch that re-enters region 0 waits for all earlier kernels before it lets the next
       // launch start (sync_first): a region is reused one full rotation later, and between any launch and
       // its region's previous user lies such a sync point, so the earlier user has always completed.
@@ -460,6 +460,13 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     }
   }
 
+  // ---- FQB_DECODE_HISTORY_STABLE: the default geometry below, but every warp requests its first pages
+  // BEFORE it waits for the kernel in front. Nothing but the page ring is touched before that wait (the
+  // scratch, q and `out` after it), so the scratch needs no rotation. A call that needs several launches
+  // (5, 6, 7 ... heads) lets only the first one start early: the later ones follow a launch of this same
+  // call, which writes the cache.
+  if ((flags & FQB_DECODE_HISTORY_STABLE) && pdl_enabled()) P.mode = kDecodeWaitRows;
+
   // ---- default: the launch waits for the kernel before it after its metadata prologue ----
   // cover the local heads with launches of 8, 4, 2 or 1 heads (one launch for 8, 4, 2, 1 heads)
   for (int base = 0; base < n_kv;) {
@@ -472,6 +479,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
     if (rc != FQB_OK) return rc;
     base += took;
+    P.mode = kDecodeWaitFirst;
   }
   return FQB_OK;
 }

@@ -80,8 +80,16 @@ norm_rope_append_kernel(const NormRopeParams P) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   pdl_wait();
-  long long dst;
-  const bool ok = append_dst(P.a, m, kKidNormRope, dst);
+  // P.a.cache == nullptr: norm + rope only (the append is left to the decode kernel that follows)
+  const bool store = P.a.cache != nullptr;
+  long long dst = 0;
+  bool ok;
+  if (store) {
+    ok = append_dst(P.a, m, kKidNormRope, dst);
+  } else {
+    ok = P.a.pos[m] >= 0;
+    if (!ok) report(FQB_ERR_INDEX, kKidNormRope, P.a.pos[m]);
+  }
   __nv_bfloat16* row = const_cast<__nv_bfloat16*>(P.a.qkv) + static_cast<long long>(m) * P.a.src_stride;
   const int p = P.a.pos[m];
   const float2 cs = ok ? __ldg(reinterpret_cast<const float2*>(P.cos_tab + static_cast<long long>(p) * 64) + lane)
@@ -118,14 +126,14 @@ norm_rope_append_kernel(const NormRopeParams P) {
     if (ok) {
       *reinterpret_cast<__nv_bfloat162*>(v + 2 * lane) = out_lo;
       *reinterpret_cast<__nv_bfloat162*>(v + 64 + 2 * lane) = out_hi;
-      if (is_k) {
+      if (is_k && store) {
         __nv_bfloat16* c = P.a.cache + dst + (hd - P.q_heads) * kHd;
         *reinterpret_cast<__nv_bfloat162*>(c + 2 * lane) = out_lo;
         *reinterpret_cast<__nv_bfloat162*>(c + 64 + 2 * lane) = out_hi;
       }
     }
   }
-  if (!ok) return;
+  if (!ok || !store) return;
   const int vecs = P.a.row_elems / 8;
   const long long plane = static_cast<long long>(kTok) * P.a.row_elems;
   for (int i = threadIdx.x; i < vecs; i += blockDim.x)

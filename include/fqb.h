@@ -81,7 +81,9 @@ int fqb_kv_append(void* cache, int num_blocks, int kv_heads_local, const void* q
  * untouched V to the cache as fqb_kv_append does -- one pass over the rows instead of two.
  * replaces: the pair of calls at engine/src/model_runtime.cu:263-268.
  * q_heads_local / kv_heads_local heads starting at element offsets q_off / k_off / v_off.
- * cos_tab / sin_tab are [n_pos][64] fp32 tables (engine/src/model_runtime.cu:111-126). */
+ * cos_tab / sin_tab are [n_pos][64] fp32 tables (engine/src/model_runtime.cu:111-126).
+ * cache == NULL: RMSNorm + RoPE only, nothing is stored (LaunchHeadNormRope by itself) -- for a
+ * pure-decode step whose append happens inside fqb_append_attn_decode. */
 int fqb_norm_rope_append(void* cache, int num_blocks, int kv_heads_local, int q_heads_local,
                          void* qkv, int src_stride, int q_off, int k_off, int v_off,
                          const float* wq, const float* wk, const float* cos_tab,
@@ -170,8 +172,8 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
  *       while that kernel still runs and waits for it only before it reads the rows -- the dependency
  *       the engine's layer loop really has (the kernel in front is the QKV projection or the q/k norm,
  *       engine/src/model_runtime.cu:259-265; the layer's cache was last written one step earlier).
- *       Scratch regions rotate as for FQB_DECODE_INDEPENDENT. Not valid directly after a kernel that
- *       writes this cache (fqb_copy_blocks, fqb_kv_append, fqb_scatter_blocks): use flags = 0 there. */
+ *       Not valid directly after a kernel that writes this cache (fqb_copy_blocks, fqb_kv_append,
+ *       fqb_scatter_blocks): use flags = 0 there. */
 #define FQB_DECODE_HISTORY_STABLE 2u
 int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
                            int q_off, int k_off, int v_off, void* out, int head_dim, const int32_t* pos,
@@ -315,6 +317,58 @@ int fqb_cow_prepare(fqb_alloc* a, int32_t* table, int pos, int32_t* pair);
 int fqb_step_pack(const int32_t* req_index, int n_rows, int n_req, const int32_t* const* tables,
                   const int32_t* table_len, int bt_stride, int32_t* bt_out, int32_t* qstart,
                   int32_t* qlen, int32_t* decode_rids, int32_t* prefill_rids, int32_t* counts);
+
+/* ---- host side: step driver -----------------------------------------------------------------------
+ * The engine's scheduling loop and the attention part of its per-step runtime, driven through the
+ * operators above. replaces: engine/src/scheduler.cc:59-154 and engine/src/scheduler.h:19-118 (Request,
+ * Grow with preempt-by-recompute, Refill, BuildBatch under a token budget, Step), and of
+ * engine/src/model_runtime.cu the input preparation (:47-108, here ONE pinned buffer and one copy for all
+ * step metadata instead of eight), RunLayers (:227-233: pure-decode steps replayed from CUDA graphs keyed
+ * (rows, decode requests), engine/src/model_runtime.h:160-201) and the attention calls of RunLayersBody
+ * (:259-283). The model is not part of it: `rows` stands in for embedding + QKV projection and fills the
+ * step's fused qkv rows (bf16 bits) for every layer, rows_host[layer * row_capacity + row][row_elems];
+ * `sample` stands in for everything after attention: it receives the attention output of every layer,
+ * out_host[layer * row_capacity + row][q_heads*128], and writes one token per entry of logits_rows.
+ * Both run on the calling thread inside fqb_driver_step. The caller owns the per-layer caches
+ * ([num_blocks][2][16][kv_heads*128] bf16 each); fqb_driver_create allocates the driver's own staging
+ * buffers once, steps allocate nothing. A pure-decode step runs, per layer, RMSNorm + RoPE and then
+ * fqb_append_attn_decode (FQB_DECODE_HISTORY_STABLE); a mixed step fqb_norm_rope_append, fqb_attn_decode
+ * and fqb_attn_prefill. One thread drives a handle, like the engine thread. */
+typedef struct fqb_driver fqb_driver;
+typedef struct fqb_driver_config {
+  int32_t n_layers, num_blocks, kv_heads, q_heads;
+  int32_t n_slots;        /* concurrent sequences, engine/src/args.h:14 */
+  int32_t token_budget;   /* rows per step, engine/src/args.h:16          */
+  int32_t prefill_chunk;  /* engine/src/args.h:17                          */
+  int32_t max_ctx;
+  int32_t use_prefix_cache, use_graphs;
+  float scale, rms_eps, rope_theta;
+} fqb_driver_config;
+typedef struct fqb_step_view {   /* all pointers: host, valid during the callback */
+  int32_t step, n_rows, n_req, n_decode, n_prefill, prefill_max_qlen, bt_stride, row_capacity, from_graph, n_logits;
+  const int32_t *tokens, *pos, *req, *qstart, *qlen, *decode_rids, *prefill_rids, *bt, *logits_rows, *request_ids;
+} fqb_step_view;
+typedef struct fqb_driver_stats {
+  uint64_t steps, graph_captures, graph_replays, preemptions, over_capacity, prefix_hit_blocks, finished, decode_rows,
+      prefill_rows;
+  int32_t free_blocks, running, waiting;
+} fqb_driver_stats;
+typedef void (*fqb_rows_fn)(void* user, int step, int n_rows, const int32_t* tokens, const int32_t* pos,
+                            const int32_t* req, uint16_t* rows_host, int row_capacity);
+typedef void (*fqb_sample_fn)(void* user, const fqb_step_view* view, const uint16_t* out_host, int32_t* sampled);
+
+/* replaces: RopeTables::Build, engine/src/model_runtime.cu:111-126 (host arrays [n_pos][head_dim/2]) */
+void fqb_rope_tables(float* cos_tab, float* sin_tab, int n_pos, int head_dim, float theta);
+int fqb_driver_create(const fqb_driver_config* cfg, void* const* layer_caches /* host array of device pointers */,
+                      const float* wq, const float* wk /* host, 128 each: q / k norm weights */, fqb_rows_fn rows,
+                      fqb_sample_fn sample, void* user, fqb_driver** out);
+void fqb_driver_destroy(fqb_driver* d);
+/* Scheduler::Submit: queues a request; returns its id (>= 0) or a negative code. */
+int fqb_driver_submit(fqb_driver* d, const int32_t* prompt, int n_prompt, int max_new);
+int fqb_driver_busy(const fqb_driver* d);
+/* Scheduler::Step: 1 = a step ran, 0 = nothing to run, negative = error (the step is lost). */
+int fqb_driver_step(fqb_driver* d);
+int fqb_driver_get_stats(const fqb_driver* d, fqb_driver_stats* out);
 
 #ifdef __cplusplus
 }

@@ -181,3 +181,29 @@ def test_step_pack_mixed_step_shape_of_config5():
     assert got["qstart"][240] == 240 and list(got["prefill_rids"]) == [240]
     with pytest.raises(fq.FqbError):
         fq.step_pack(np.asarray([0, 5], np.int32), 2)
+
+
+def test_rope_tables_match_the_oracle_bit_for_bit():
+    """fqb_rope_tables restates RopeTables::Build (engine/src/model_runtime.cu:111-126); the oracle's
+    own restatement must give the same bits, because the step driver normalises with the former and the
+    tests mirror it with the latter."""
+    import oracle_lib as O
+
+    a, b = fq.rope_tables(700), O.rope_tables(700)
+    assert np.array_equal(a[0].view(np.uint32), b[0].view(np.uint32))
+    assert np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+
+
+def test_driver_refuses_bad_configurations_without_a_gpu():
+    from flashqwen_b200 import driver
+
+    noop_rows = lambda *a: None  # noqa: E731
+    with pytest.raises(fq.FqbError) as e:   # 8 blocks cannot hold one sequence of 512 tokens
+        fq.StepDriver([0], np.ones(128), np.ones(128), noop_rows, noop_rows, num_blocks=8, kv_heads=2, n_slots=2,
+                      token_budget=32, prefill_chunk=16, max_ctx=512)
+    assert e.value.code == -7
+    with pytest.raises(fq.FqbError) as e:
+        fq.StepDriver([0], np.ones(128), np.ones(128), noop_rows, noop_rows, num_blocks=64, kv_heads=2, n_slots=0,
+                      token_budget=32, prefill_chunk=16, max_ctx=512)
+    assert e.value.code == -1
+    assert driver.DriverStats is not None
