@@ -280,6 +280,15 @@ class FqbRunner:
                                    PAGE, w.scale, self.pm, self.pl, self.pa, self.slots, None, flags)
         self._count_decode(flags)
 
+    def fused_gather(self, layer, qkv, bt, pos, qstart, rids, desc, flags):
+        """The fused call that also stores the finished rows into every rank's buffer of full rows."""
+        w = self.w
+        self.fq.append_attn_decode_gather(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, 0, w.k_off, w.v_off,
+                                          w.out[layer], HD, pos, qstart, rids, self.plan if self.use_plan else None,
+                                          w.batch, bt, w.max_blocks, PAGE, w.scale, self.pm, self.pl, self.pa, self.slots,
+                                          desc, None, flags)
+        self.launches += 1
+
     def append(self, layer, qkv, bt, req, pos):
         w = self.w
         self.fq.kv_append(w.pools[layer], w.num_blocks, w.kvl, qkv[layer], w.row_dim, w.k_off, w.v_off, bt, w.max_blocks,
@@ -728,19 +737,70 @@ def main():
     achieved = w.bytes_layer_rank / layer_s / 1e9
 
     # ---- attention + reassembly of the per-head outputs on every GPU (N > 1) ----
-    gather = None
+    # Every rank owns a buffer of full rows [layers][batch][4096] that all ranks map (CUDA IPC); the decode
+    # kernel stores each finished row into all of them and publishes per layer; a one-warp kernel per layer
+    # stands for the consumer's wait. Where IPC is not available the old way remains: one NCCL all-gather
+    # per layer, launched from the host.
+    gather, peers, descs, ipc_error = None, None, None, ""
     if dist_on:
-        gathered = torch.empty((world, a.batch, w.hl * HD), dtype=torch.bfloat16, device=dev)
+        from flashqwen_b200 import peer
+        try:
+            mem = peer.PeerMemory(a.layers * a.batch * Q_DIM * 2, a.layers, world)
 
-        def step_gather():
-            r.make_plan(w.pos, w.qstart, w.rids)
-            for layer in range(a.layers):
-                r.fused(layer, w.qkv, w.bt, w.req, w.pos, w.qstart, w.rids, flags=HISTORY_STABLE)
-                torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
+            def exchange(obj):
+                every = [None] * world
+                torch.distributed.all_gather_object(every, obj)
+                return every
 
-        g_ms = time_region(step_gather, a.steps, a.warmup, dist_on, dev) / a.steps
+            peers = peer.PeerGroup(rank, world, mem, exchange=exchange)
+            # generous limit on the waits: ranks drift by whole graph instantiations during warm-up
+            descs = [peers.desc(slot=layer, byte_offset=layer * a.batch * Q_DIM * 2, timeout_ms=5000)
+                     for layer in range(a.layers)]
+            full_rows = mem.as_tensor(dev).view(a.layers, a.batch, Q_DIM)
+        except Exception as e:  # noqa: BLE001 -- no IPC between these processes: fall back to NCCL
+            peers, descs, ipc_error = None, None, repr(e)
+        ok = torch.tensor([1 if peers is not None else 0], device=dev)
+        torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            peers = descs = None
+
+        if peers is not None:
+            def step_gather():
+                r.make_plan(w.pos, w.qstart, w.rids)
+                for layer in range(a.layers):
+                    r.fused_gather(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, descs[layer], INDEPENDENT)
+                    r.fq.gather_wait(descs[layer])
+                    r.launches += 1
+            how = ("rows stored into every rank's buffer of full rows by the decode kernel itself (peer stores over "
+                   "NVLink, FQB_DECODE_INDEPENDENT), one publish and one wait kernel per layer")
+        else:
+            gathered = torch.empty((world, a.batch, w.hl * HD), dtype=torch.bfloat16, device=dev)
+
+            def step_gather():
+                r.make_plan(w.pos, w.qstart, w.rids)
+                for layer in range(a.layers):
+                    r.fused(layer, w.qkv, w.bt, w.req, w.pos, w.qstart, w.rids, flags=INDEPENDENT)
+                    torch.distributed.all_gather_into_tensor(gathered, w.out[layer])
+            how = ("one NCCL all-gather per layer, launched from the host after that layer's kernel (no CUDA IPC between "
+                   "these processes" + (": " + ipc_error if ipc_error else "") + ")")
+
+        run_g = step_gather
+        if a.graph and peers is not None:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_gather()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg):
+                step_gather()
+            run_g = gg.replay
+        g_ms = time_region(run_g, a.steps, a.warmup, dist_on, dev) / a.steps
+        r.check()
         gather = {"ms_per_step": round(g_ms, 4), "value": round(w.bytes_layer_total * a.layers / (g_ms * 1e-3) / 1e9, 2),
-                  "how": "one NCCL all-gather per layer, launched from the host after that layer's kernel"}
+                  "how": how}
 
     # ---- end to end from host buffers ----
     e2e, e2e_ind, check = None, None, None
@@ -769,7 +829,8 @@ def main():
         ev_in = [torch.cuda.Event() for _ in chunks]
         ev_out = [torch.cuda.Event() for _ in chunks]
 
-        gathered_all = torch.empty((world, w.out.numel()), dtype=torch.bfloat16, device=dev) if dist_on else None
+        gathered_all = (torch.empty((world, w.out.numel()), dtype=torch.bfloat16, device=dev)
+                        if dist_on and peers is None else None)
 
         def step_core(flags=HISTORY_STABLE):
             """Copies in, the fused append + attention per layer, and the chunked copy back of this rank's outputs."""
@@ -787,11 +848,16 @@ def main():
                     r.make_plan(d_pos, d_qstart, d_rids)
                 for layer in range(l0, l1):
                     # a chunk's first launch follows a copy that wrote its rows: an event wait orders it in full
-                    r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=flags)
+                    if peers is not None:
+                        r.fused_gather(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids, descs[layer], flags)
+                    else:
+                        r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=flags)
                 ev_out[i].record(main)
                 with torch.cuda.stream(copy_out):
                     copy_out.wait_event(ev_out[i])
                     w.h_out[l0:l1].copy_(w.out[l0:l1], non_blocking=True)
+            if peers is not None:
+                r.fq.gather_wait_all(descs[0])   # every rank's rows of every layer are in this rank's buffer
             main.wait_stream(copy_out)
 
         def time_e2e(flags):
@@ -813,8 +879,7 @@ def main():
 
             def step_e2e_sync():
                 core()
-                if dist_on:  # per-head outputs of all layers reassembled on the GPUs by ONE all-gather (the host
-                    #          has read this rank's heads chunk by chunk inside the step already)
+                if dist_on and peers is None:  # no IPC: per-head outputs of all layers reassembled by ONE all-gather
                     torch.distributed.all_gather_into_tensor(gathered_all, w.out.view(-1))
                 torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
@@ -835,11 +900,17 @@ def main():
                            "and of the step metadata (one pinned buffer, one copy), per layer "
                            + ("the reference's KV append + decode attention" if reference else
                               "the fused KV append + decode attention (FQB_DECODE_HISTORY_STABLE)")
-                           + (", one NCCL all-gather of all layers' head outputs" if dist_on else "") + ", D2H of the output"
+                           + ((", every finished row stored into all ranks' buffers of full rows by the kernel, one wait "
+                               "for all layers at the end") if dist_on and peers is not None else
+                              (", one NCCL all-gather of all layers' head outputs" if dist_on else ""))
+                           + ", D2H of the output"
                            + ("; one CUDA graph per step, host sync every step" if a.graph else "")}
         if dist_on:
             # the reassembled rows of layer 0 against the oracle, outside the timed region
-            lay0 = gathered_all.view(world, a.layers, a.batch, w.hl * HD)[:, 0].permute(1, 0, 2).reshape(a.batch, Q_DIM)
+            if peers is not None:
+                lay0 = full_rows[0].view(torch.bfloat16)
+            else:
+                lay0 = gathered_all.view(world, a.layers, a.batch, w.hl * HD)[:, 0].permute(1, 0, 2).reshape(a.batch, Q_DIM)
             check = gather_check(w, a, world, rank, lay0, dev)
 
     if rank != 0:
@@ -866,7 +937,7 @@ def main():
     if "dependent" in modes:
         line["roofline_dependent"] = dict(modes["dependent"]["roofline"], bound="hbm", unit="GB/s")
     if gather is not None:
-        line["with_all_gather"] = gather
+        line["with_all_gather"] = gather   # attention + reassembly of full rows on every GPU, per layer
     if e2e is not None:
         line["e2e"] = e2e
         if e2e_ind is not None:

@@ -8,12 +8,14 @@ operator raises if the library is missing.
 """
 from ._lib import FqbError, lib, library_path  # noqa: F401
 from .driver import StepDriver, rope_tables  # noqa: F401
+from . import peer  # noqa: F401
 from .host import BlockAllocator, acquire_prefix, cache_blocks, cow_prepare, hash_block, step_pack  # noqa: F401
 from .ops import (  # noqa: F401
     DECODE_HISTORY_STABLE,
     DECODE_INDEPENDENT,
     KvStore,
     append_attn_decode,
+    append_attn_decode_gather,
     attn_decode,
     attn_decode_plan,
     attn_decode_planned,
@@ -25,6 +27,8 @@ from .ops import (  # noqa: F401
     device_status,
     device_status_reset,
     gather_blocks,
+    gather_wait,
+    gather_wait_all,
     kv_append,
     norm_rope_append,
     scatter_blocks,

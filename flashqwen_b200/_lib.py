@@ -57,6 +57,16 @@ SIGNATURES = {
     "fqb_driver_busy": (_i, [_p]),
     "fqb_driver_step": (_i, [_p]),
     "fqb_driver_get_stats": (_i, [_p, _p]),
+    "fqb_append_attn_decode_gather": (_i, [_p, _i, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p, _i, _p, _i, _i, _f, _p,
+                                           _p, _p, _i64, C.c_uint, _p, _p]),
+    "fqb_gather_control_bytes": (_i64, [_i, _i]),
+    "fqb_gather_wait": (_i, [_p, _p]),
+    "fqb_gather_wait_all": (_i, [_p, _p]),
+    "fqb_peer_alloc": (_i, [_i64, _p]),
+    "fqb_peer_free": (_i, [_p]),
+    "fqb_peer_export": (_i, [_p, _p]),
+    "fqb_peer_open": (_i, [_p, _p]),
+    "fqb_peer_close": (_i, [_p]),
     "fqb_attn_decode_static": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
     "fqb_attn_prefill": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
     "fqb_copy_blocks": (_i, [_p, _i, _i, _p, _i, _p]),

@@ -23,7 +23,7 @@ constexpr int kHalfBytes = kPlaneBytes / 2;         // 2048
 
 // ids written to the status word so a failure names its kernel
 enum KernelId { kKidAppend = 1, kKidDecode = 2, kKidCombine = 3, kKidPrefill = 4, kKidBlocks = 5,
-                kKidNormRope = 6 };
+                kKidNormRope = 6, kKidGather = 7 };
 
 // {code, kernel id, blockIdx.x, value}; first failure wins
 __device__ int g_status[4];

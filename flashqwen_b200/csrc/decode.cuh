@@ -35,6 +35,8 @@
 
 namespace fqb {
 
+constexpr int kMaxPeers = 8;
+
 struct DecodeParams {
   const __nv_bfloat16* q;
   int q_stride;
@@ -60,6 +62,17 @@ struct DecodeParams {
   // seen from q: K of cache head kvh at q + k_rel + kvh*128, V at q + v_rel + kvh*128.
   __nv_bfloat16* cache_w;
   long long k_rel, v_rel;
+  // Reassembly over G GPUs (n_peers == 0: none). A finished row also goes to every rank's buffer
+  // peer_out[r] of full rows [rows][peer_heads][128] at head column peer_col + (local head); plain
+  // stores, the pointers may be peer memory. When the last warp of the launch has arrived on `arrive`
+  // it bumps this rank's publish counter seq and stores the new value into every rank's flag word
+  // peer_flag[r] (release, system scope): "rank `rank` has delivered publish number v of this slot".
+  int n_peers;
+  __nv_bfloat16* peer_out[kMaxPeers];
+  unsigned* peer_flag[kMaxPeers];
+  int peer_heads, peer_col;
+  unsigned* seq;
+  unsigned long long* arrive;
 };
 
 // What a launch waits for before it touches anything but the step metadata:
@@ -174,13 +187,20 @@ __device__ __forceinline__ void merge_pair(const DecodeParams& P, int di, int kv
     }
   }
   const float inv = gl > 0.f ? 1.f / gl : 0.f;
-  __nv_bfloat16* o = P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd + dbase;
+  uint2 pk[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint2 pk;
-    pk.x = pack_bf16(acc[i].x * inv, acc[i].y * inv);
-    pk.y = pack_bf16(acc[i].z * inv, acc[i].w * inv);
-    *reinterpret_cast<uint2*>(o + 32 * i) = pk;
+    pk[i].x = pack_bf16(acc[i].x * inv, acc[i].y * inv);
+    pk[i].y = pack_bf16(acc[i].z * inv, acc[i].w * inv);
+  }
+  __nv_bfloat16* o = P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd + dbase;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) *reinterpret_cast<uint2*>(o + 32 * i) = pk[i];
+  for (int r = 0; r < P.n_peers; ++r) {
+    __nv_bfloat16* po =
+        P.peer_out[r] + (static_cast<long long>(flat) * P.peer_heads + P.peer_col + kvh * kGroup + g) * kHd + dbase;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint2*>(po + 32 * i) = pk[i];
   }
 }
 
@@ -226,6 +246,61 @@ decode_plan_kernel(const int* __restrict__ pos, const int* __restrict__ qstart, 
   __syncthreads();
   if (di < n_decode)
     reinterpret_cast<int4*>(plan)[di] = make_int4(r, flat, qp, s_pages[di] + s_warp[warp]);
+}
+
+// Reassembly, consumer side: returns once every rank has delivered publish number seq[0] of the slot,
+// i.e. flags[r] >= this rank's own publish count (all ranks make the same calls in the same order, and
+// this kernel follows this rank's own publishing launch on the stream). One warp, lane r polls rank r's
+// word in LOCAL memory. The wait is bounded by time: past the limit it records FQB_ERR_TIMEOUT and returns.
+__global__ void __launch_bounds__(32)
+gather_wait_kernel(const unsigned* __restrict__ flags, const unsigned* __restrict__ seq, int world,
+                   unsigned long long limit_ns) {
+  pdl_launch_dependents();
+  pdl_wait();  // the publishing launch of this rank has completed: seq holds its number
+  const int lane = threadIdx.x;
+  if (lane >= world) return;
+  const unsigned want = *reinterpret_cast<const volatile unsigned*>(seq);
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (;;) {
+    unsigned have;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(flags + lane) : "memory");
+    if (static_cast<int>(have - want) >= 0) return;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    if (now - t0 > limit_ns) {
+      report(FQB_ERR_TIMEOUT, kKidGather, lane);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+// The same for every slot of the control block, one after the other (at the end of a step).
+__global__ void __launch_bounds__(32)
+gather_wait_all_kernel(const unsigned* __restrict__ flags, const unsigned* __restrict__ seq, int slots, int world,
+                       unsigned long long limit_ns) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x;
+  if (lane >= world) return;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (int s = 0; s < slots; ++s) {
+    const unsigned want = *reinterpret_cast<const volatile unsigned*>(seq + s);
+    for (;;) {
+      unsigned have;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(flags + s * world + lane) : "memory");
+      if (static_cast<int>(have - want) >= 0) break;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now - t0 > limit_ns) {
+        report(FQB_ERR_TIMEOUT, kKidGather, s * 16 + lane);
+        return;
+      }
+      __nanosleep(200);
+    }
+  }
 }
 
 // HEADS = local kv heads served by the launch (1, 2, 4 or 8); the CTA's NW warps form SUB = NW / HEADS
@@ -390,6 +465,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       if (s_qpos[di] < 0) {  // no key at all: the row is zero (the reference's inv = 0 case)
         uint4* o = reinterpret_cast<uint4*>(P.out + static_cast<long long>(s_flat[di]) * P.n_heads * kHd);
         for (int i = 0; i < P.n_heads * kHd / 8; ++i) o[i] = make_uint4(0, 0, 0, 0);
+        for (int r = 0; r < P.n_peers; ++r) {
+          uint4* po = reinterpret_cast<uint4*>(
+              P.peer_out[r] + (static_cast<long long>(s_flat[di]) * P.peer_heads + P.peer_col) * kHd);
+          for (int i = 0; i < P.n_heads * kHd / 8; ++i) po[i] = make_uint4(0, 0, 0, 0);
+        }
       }
 
   // ---- consumer ----
@@ -519,10 +599,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       // the pair lies inside this segment: straight from registers to `out`
       if (g < kGroup) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
         uint32_t* dst = reinterpret_cast<uint32_t*>(
             P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j * 4 + t] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
+        for (int j = 0; j < 16; ++j) dst[j * 4 + t] = w[j];
+        for (int r = 0; r < P.n_peers; ++r) {
+          uint32_t* pd = reinterpret_cast<uint32_t*>(
+              P.peer_out[r] + (static_cast<long long>(flat) * P.peer_heads + P.peer_col + kvh * kGroup + g) * kHd);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pd[j * 4 + t] = w[j];
+        }
       }
     } else {
       const int b0 = s_cum[cc.di] / W, b1 = (s_cum[cc.di] + cc.np - 1) / W;  // segments that see this sequence
@@ -556,6 +645,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     for (int ks = 0; ks < 8; ++ks) {
       qa[ks][0] = qn[ks][0];
       qa[ks][1] = qn[ks][1];
+    }
+  }
+  // ---- reassembly: tell every rank that this rank's rows of the launch are in its buffer ----
+  if (P.n_peers > 0) {
+    __threadfence_system();  // this thread's stores to the peers are performed before its warp arrives
+    __syncwarp();
+    if (lane == 0 && take_ticket_is_last(P.arrive, P.epoch, static_cast<int>(gridDim.x) * NW)) {
+      *P.arrive = 0ull;  // ready for a replay with the same launch number
+      const unsigned v = atomicAdd(P.seq, 1u) + 1u;
+      __threadfence_system();
+      for (int r = 0; r < P.n_peers; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flag[r]), "r"(v) : "memory");
     }
   }
   // A kernel never completes before the one launched ahead of it: one warp of CTA 0 stays until that

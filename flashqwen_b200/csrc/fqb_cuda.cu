@@ -151,6 +151,11 @@ constexpr int kDefaultCtas = FQB_DEFAULT_CTAS_PER_SM;
 // (default mode only), 4, 2 and 1 heads. Default mode: one CTA per SM for the 8-head shape, two for the
 // others; overlapped modes: one CTA per SM. The scratch is indexed with the call's n_kv, so the largest
 // launch decides.
+// Layout of a rank's reassembly control block (32-bit words): flags [slots][world] | publish counters
+// [slots] | arrival words [slots] (64-bit, 8-byte aligned).
+size_t gather_seq_offset(int slots, int world) { return static_cast<size_t>(slots) * world; }
+size_t gather_arrive_offset(int slots, int world) { return (gather_seq_offset(slots, world) + slots + 1) & ~size_t(1); }
+
 int max_segments(int n_kv, int sm_count, bool overlapped) {
   int seg = 0, left = n_kv;
   const int per = overlapped ? 1 : kDefaultCtas;
@@ -380,8 +385,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
                        int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
-                       const int32_t* plan, void* cache_w, long long k_rel, long long v_rel, void* stream) {
-  if (n_decode <= 0) return FQB_OK;
+                       const int32_t* plan, void* cache_w, long long k_rel, long long v_rel, const fqb_gather* gather,
+                       void* stream) {
+  if (n_decode <= 0 && !gather) return FQB_OK;
   if (plan && (n_decode > 256 || (reinterpret_cast<uintptr_t>(plan) & 15u)))
     return set_error(FQB_ERR_INVALID, "attn_decode: a step plan serves at most 256 sequences per call and must be 16-byte aligned");
   if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
@@ -424,6 +430,29 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   P.cache_w = static_cast<__nv_bfloat16*>(cache_w);
   P.k_rel = k_rel;
   P.v_rel = v_rel;
+  P.n_peers = 0;
+  if (gather) {
+    const fqb_gather& g = *gather;
+    if (g.world < 1 || g.world > kMaxPeers || g.rank < 0 || g.rank >= g.world || g.slot < 0 || g.slot >= g.slots ||
+        !g.control)
+      return set_error(FQB_ERR_INVALID, "attn_decode: bad reassembly descriptor (world %d, rank %d, slot %d of %d)",
+                       g.world, g.rank, g.slot, g.slots);
+    if (n_decode <= 0 || n_decode > 256 || (n_kv != 1 && n_kv != 2 && n_kv != 4))
+      return set_error(FQB_ERR_SHAPE, "attn_decode: reassembly takes calls that go out as ONE launch: 1 to 256 "
+                                      "sequences and 1, 2 or 4 local kv heads (got %d, %d)", n_decode, n_kv);
+    P.n_peers = g.world;
+    for (int r = 0; r < g.world; ++r) {
+      if (!g.out[r] || !g.flags[r] || !aligned16(g.out[r]))
+        return set_error(FQB_ERR_INVALID, "attn_decode: reassembly pointer of rank %d missing or misaligned", r);
+      P.peer_out[r] = static_cast<__nv_bfloat16*>(g.out[r]);
+      P.peer_flag[r] = static_cast<unsigned*>(g.flags[r]) + static_cast<size_t>(g.slot) * g.world + g.rank;
+    }
+    P.peer_heads = g.world * n_heads;
+    P.peer_col = g.rank * n_heads;
+    unsigned* ctl = static_cast<unsigned*>(g.control);
+    P.seq = ctl + gather_seq_offset(g.slots, g.world) + g.slot;
+    P.arrive = reinterpret_cast<unsigned long long*>(ctl + gather_arrive_offset(g.slots, g.world)) + g.slot;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // ---- launches that wait for nothing: one CTA per SM per launch, two launches resident side by side ----
@@ -493,7 +522,7 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
     return set_error(FQB_ERR_INVALID, "attn_decode: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode "
                                       "(a separate append kernel in front writes the cache this call reads)");
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
-                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, stream);
+                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, nullptr, stream);
 }
 
 int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -505,7 +534,7 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
     return set_error(FQB_ERR_INVALID, "attn_decode_planned: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode");
   // pos / qstart / decode_rids are not read when a plan is given; the plan pointer stands in for them
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, plan, plan, plan, n_decode, bt,
-                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, nullptr, 0, 0, stream);
+                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, nullptr, 0, 0, nullptr, stream);
 }
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -516,12 +545,12 @@ int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_bloc
                             n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, 0u, stream);
 }
 
-int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,
-                           int k_off, int v_off, void* out, int head_dim, const int32_t* pos, const int32_t* qstart,
-                           const int32_t* decode_rids, const int32_t* plan, int n_decode, const int32_t* bt,
-                           int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
-                           int64_t partial_slots, unsigned flags, void* stream) {
-  if (n_decode <= 0) return FQB_OK;
+static int append_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,
+                         int k_off, int v_off, void* out, int head_dim, const int32_t* pos, const int32_t* qstart,
+                         const int32_t* decode_rids, const int32_t* plan, int n_decode, const int32_t* bt,
+                         int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
+                         int64_t partial_slots, unsigned flags, const fqb_gather* gather, void* stream) {
+  if (n_decode <= 0 && !gather) return FQB_OK;
   if (!qkv) return set_error(FQB_ERR_INVALID, "append_attn_decode: null pointer");
   if (!aligned16(qkv) || (src_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8) || q_off < 0 || k_off < 0 || v_off < 0)
     return set_error(FQB_ERR_INVALID, "append_attn_decode: qkv, src_stride, q_off, k_off and v_off must keep 16-byte alignment");
@@ -533,7 +562,86 @@ int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, cons
   const int32_t* m2 = plan ? plan : decode_rids;
   return decode_impl(q, src_stride, cache, num_blocks, out, kv_heads_local * kGroup, kv_heads_local, head_dim, m0, m1, m2,
                      n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, cache,
-                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, stream);
+                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, gather, stream);
+}
+
+int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,
+                           int k_off, int v_off, void* out, int head_dim, const int32_t* pos, const int32_t* qstart,
+                           const int32_t* decode_rids, const int32_t* plan, int n_decode, const int32_t* bt,
+                           int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
+                           int64_t partial_slots, unsigned flags, void* stream) {
+  return append_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos, qstart,
+                       decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags,
+                       nullptr, stream);
+}
+
+int fqb_append_attn_decode_gather(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                                  int q_off, int k_off, int v_off, void* out, int head_dim, const int32_t* pos,
+                                  const int32_t* qstart, const int32_t* decode_rids, const int32_t* plan, int n_decode,
+                                  const int32_t* bt, int max_blocks, int block_size, float scale, float* pm, float* pl,
+                                  float* pa, int64_t partial_slots, unsigned flags, const fqb_gather* gather,
+                                  void* stream) {
+  if (!gather) return set_error(FQB_ERR_INVALID, "append_attn_decode_gather: null reassembly descriptor");
+  return append_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos, qstart,
+                       decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags,
+                       gather, stream);
+}
+
+int64_t fqb_gather_control_bytes(int slots, int world) {
+  if (slots <= 0 || world <= 0 || world > kMaxPeers) return 0;
+  return static_cast<int64_t>(gather_arrive_offset(slots, world)) * 4 + static_cast<int64_t>(slots) * 8;
+}
+
+int fqb_gather_wait(const fqb_gather* g, void* stream) {
+  if (!g || !g->control || g->world < 1 || g->world > kMaxPeers || g->slot < 0 || g->slot >= g->slots)
+    return set_error(FQB_ERR_INVALID, "gather_wait: bad reassembly descriptor");
+  const unsigned* ctl = static_cast<const unsigned*>(g->control);
+  const unsigned long long limit_ns = static_cast<unsigned long long>(g->timeout_ms > 0 ? g->timeout_ms : 1000) * 1000000ull;
+  FQB_CUDA_TRY(launch_ex(gather_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), true,
+                         ctl + static_cast<size_t>(g->slot) * g->world, ctl + gather_seq_offset(g->slots, g->world) + g->slot,
+                         g->world, limit_ns));
+  return FQB_OK;
+}
+
+int fqb_gather_wait_all(const fqb_gather* g, void* stream) {
+  if (!g || !g->control || g->world < 1 || g->world > kMaxPeers || g->slots < 1)
+    return set_error(FQB_ERR_INVALID, "gather_wait_all: bad reassembly descriptor");
+  const unsigned* ctl = static_cast<const unsigned*>(g->control);
+  const unsigned long long limit_ns = static_cast<unsigned long long>(g->timeout_ms > 0 ? g->timeout_ms : 1000) * 1000000ull;
+  FQB_CUDA_TRY(launch_ex(gather_wait_all_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), true, ctl,
+                         ctl + gather_seq_offset(g->slots, g->world), g->slots, g->world, limit_ns));
+  return FQB_OK;
+}
+
+// ---- set-up helpers for the reassembly buffers: memory another process on this node can map ----
+int fqb_peer_alloc(int64_t bytes, void** ptr) {
+  if (bytes <= 0 || !ptr) return set_error(FQB_ERR_INVALID, "peer_alloc: bad arguments");
+  FQB_CUDA_TRY(cudaMalloc(ptr, static_cast<size_t>(bytes)));
+  FQB_CUDA_TRY(cudaMemset(*ptr, 0, static_cast<size_t>(bytes)));
+  return FQB_OK;
+}
+int fqb_peer_free(void* ptr) {
+  if (ptr) FQB_CUDA_TRY(cudaFree(ptr));
+  return FQB_OK;
+}
+int fqb_peer_export(void* ptr, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == FQB_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle64) return set_error(FQB_ERR_INVALID, "peer_export: null pointer");
+  cudaIpcMemHandle_t h;
+  FQB_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+  std::memcpy(handle64, &h, sizeof h);
+  return FQB_OK;
+}
+int fqb_peer_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return set_error(FQB_ERR_INVALID, "peer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof h);
+  FQB_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return FQB_OK;
+}
+int fqb_peer_close(void* ptr) {
+  if (ptr) FQB_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return FQB_OK;
 }
 
 // ---- decode attention for callers that cannot provide scratch -------------------------------------

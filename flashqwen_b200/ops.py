@@ -97,6 +97,28 @@ def append_attn_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off
           "fqb_append_attn_decode")
 
 
+def append_attn_decode_gather(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos,
+                              qstart, decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa,
+                              partial_slots, gather, stream=None, flags=0):
+    """fqb_append_attn_decode_gather: the fused call that also stores every finished row into all ranks'
+    buffers of full rows and publishes (gather: a peer.Gather descriptor)."""
+    check(lib.fqb_append_attn_decode_gather(_ptr(cache), num_blocks, kv_heads_local, _ptr(qkv), src_stride, q_off, k_off,
+                                            v_off, _ptr(out), head_dim, _ptr(pos), _ptr(qstart), _ptr(decode_rids),
+                                            _ptr(plan), n_decode, _ptr(bt), max_blocks, block_size, scale, _ptr(pm),
+                                            _ptr(pl), _ptr(pa), partial_slots, flags, C.addressof(gather),
+                                            _stream(stream)), "fqb_append_attn_decode_gather")
+
+
+def gather_wait(gather, stream=None):
+    """fqb_gather_wait: one-warp kernel that returns once every rank has delivered the slot's current publish."""
+    check(lib.fqb_gather_wait(C.addressof(gather), _stream(stream)), "fqb_gather_wait")
+
+
+def gather_wait_all(gather, stream=None):
+    """fqb_gather_wait_all: the same wait over every slot of the control block."""
+    check(lib.fqb_gather_wait_all(C.addressof(gather), _stream(stream)), "fqb_gather_wait_all")
+
+
 def attn_decode_static(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                        n_decode, bt, max_blocks, block_size, scale, stream=None):
     """fqb_attn_decode_static: decode attention with the library's built-in scratch, for callers that

@@ -181,6 +181,49 @@ int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, cons
                            const int32_t* bt, int max_blocks, int block_size, float scale, float* pm, float* pl,
                            float* pa, int64_t partial_slots, unsigned flags, void* stream);
 
+/* ---- reassembly of the per-head outputs over G GPUs of one node, inside the decode kernel -----------
+ * No reference counterpart (the reference is single-GPU). With the KV heads sharded over G GPUs every
+ * rank produces [rows][(32/G)*128]; where full rows are wanted on every GPU, the kernel that finishes a
+ * row stores it straight into every rank's buffer of full rows [rows][32*128] (plain stores over
+ * NVLink into peer memory, no multicast, no library kernel on peer memory), instead of a separate
+ * all-gather per layer afterwards. When the launch's last warp is through, the rank bumps its publish
+ * counter for the slot and stores it into every rank's flag word. fqb_gather_wait enqueues a one-warp
+ * kernel that returns once all G ranks have delivered the slot's current publish; it polls local memory
+ * only and gives up after timeout_ms (default 1000) with FQB_ERR_TIMEOUT in the device status.
+ * Set-up, once: every rank allocates its buffers and one zeroed control block of
+ * fqb_gather_control_bytes(slots, world) bytes with fqb_peer_alloc, exports them (fqb_peer_export, 64-byte
+ * handles passed through any host channel) and opens the others' (fqb_peer_open). A slot is one
+ * independent sequence of publishes (one per layer, say). All ranks make the same calls in the same
+ * order. A rank may overwrite a peer's buffer of slot s as soon as it reaches its next call for s: put the
+ * consumer of a slot (and a fqb_gather_wait) on every rank's stream before that rank's next call for it.
+ * The calls take no CUDA graph parameters that change between replays, so they can be captured. */
+#define FQB_PEER_HANDLE_BYTES 64
+typedef struct fqb_gather {
+  int32_t world, rank;   /* ranks of the node sharing the heads, this rank           */
+  int32_t slots, slot;   /* publish sequences in the control block, the one to use   */
+  void* out[8];          /* every rank's buffer of full rows for this call; out[rank] is local */
+  void* flags[8];        /* every rank's control block (its start); flags[rank] is local        */
+  void* control;         /* this rank's control block                                          */
+  int32_t timeout_ms;    /* fqb_gather_wait gives up after this long; 0 = 1000                  */
+} fqb_gather;
+int64_t fqb_gather_control_bytes(int slots, int world);
+/* fqb_append_attn_decode that also delivers the rows to every rank and publishes. One launch per call:
+ * 1..256 sequences, 1, 2 or 4 local kv heads. */
+int fqb_append_attn_decode_gather(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                                  int q_off, int k_off, int v_off, void* out, int head_dim, const int32_t* pos,
+                                  const int32_t* qstart, const int32_t* decode_rids, const int32_t* plan, int n_decode,
+                                  const int32_t* bt, int max_blocks, int block_size, float scale, float* pm, float* pl,
+                                  float* pa, int64_t partial_slots, unsigned flags, const fqb_gather* gather,
+                                  void* stream);
+int fqb_gather_wait(const fqb_gather* gather, void* stream);
+/* The same wait for every slot of the control block in one kernel (end of a step). */
+int fqb_gather_wait_all(const fqb_gather* gather, void* stream);
+int fqb_peer_alloc(int64_t bytes, void** ptr /* host: receives a zeroed device allocation */);
+int fqb_peer_free(void* ptr);
+int fqb_peer_export(void* ptr, void* handle64 /* host, FQB_PEER_HANDLE_BYTES */);
+int fqb_peer_open(const void* handle64 /* host */, void** ptr /* host: receives the mapped peer pointer */);
+int fqb_peer_close(void* ptr);
+
 /* Decode attention without caller scratch. No counterpart in the reference (its call site always
  * passes pm / pl / pa): this entry point exists for callers that have no device memory to give and
  * no way to get any at the point of the call -- an engine that handed all free VRAM to its KV pool

@@ -64,8 +64,9 @@ def test_decode_launcher_with_a_full_default_batch_of_16_sequences():
 
 
 def test_configure_refuses_a_scratch_that_cannot_serve_one_sequence():
-    # slots = 4 in the engine would give 4 096 floats: below what one launch over all SMs needs
-    assert _lib.lib.fqb_engine_configure(100, 4 * 64 * 16) == -4
+    # slots = 2 in the engine would give 2 048 floats: below what one launch over all SMs needs for any head count
+    assert _lib.lib.fqb_attn_decode_slots_needed(1, 1) > 2 * 64 * 16
+    assert _lib.lib.fqb_engine_configure(100, 2 * 64 * 16) == -4
     assert b"partial" in _lib.lib.fqb_last_error()
     assert _lib.lib.fqb_engine_configure(100, REF_SLOTS) == 0
 
