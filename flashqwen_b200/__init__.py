@@ -17,6 +17,7 @@ from .ops import (  # noqa: F401
     append_attn_decode,
     append_attn_decode_gather,
     attn_decode,
+    attn_decode_fp8,
     attn_decode_plan,
     attn_decode_planned,
     attn_decode_static,
@@ -30,6 +31,7 @@ from .ops import (  # noqa: F401
     gather_wait,
     gather_wait_all,
     kv_append,
+    kv_append_fp8,
     norm_rope_append,
     scatter_blocks,
 )

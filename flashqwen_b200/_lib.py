@@ -67,6 +67,11 @@ SIGNATURES = {
     "fqb_peer_export": (_i, [_p, _p]),
     "fqb_peer_open": (_i, [_p, _p]),
     "fqb_peer_close": (_i, [_p]),
+    "fqb_kv_pool_bytes_fp8": (_i64, [_i, _i]),
+    "fqb_kv_scale_bytes_fp8": (_i64, [_i, _i]),
+    "fqb_kv_append_fp8": (_i, [_p, _p, _i, _i, _p, _i, _i, _i, _p, _i, _p, _p, _i, _p]),
+    "fqb_attn_decode_fp8": (_i, [_p, _i, _p, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64,
+                                 C.c_uint, _p]),
     "fqb_attn_decode_static": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p]),
     "fqb_attn_prefill": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _i, _i, _f, _p]),
     "fqb_copy_blocks": (_i, [_p, _i, _i, _p, _i, _p]),

@@ -58,6 +58,7 @@ struct DecodeParams {
   int mode;        // kDecodeWaitFirst / kDecodeNoWait / kDecodeWaitRows, see below
   int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
   const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
+  const float* scales;  // fp8 cache only: [num_blocks][n_kv][2 planes][16 tokens] fp32
   // fused append of the new token (cache_w == nullptr: none). The rows are qkv + flat * q_stride
   // seen from q: K of cache head kvh at q + k_rel + kvh*128, V at q + v_rel + kvh*128.
   __nv_bfloat16* cache_w;
@@ -112,10 +113,17 @@ __device__ __forceinline__ bool take_ticket_is_last(unsigned long long* c, unsig
   return false;
 }
 
-template <int NW, int NS, int MAXD>
+// One page slice of the fp8 cache: [2 planes][16 tokens][128 e4m3 bytes] + its 32 scales.
+constexpr int kPageBytes8 = 2 * kTok * kHd;  // 4096
+constexpr int kScaleBytes8 = 2 * kTok * 4;   // 128
+constexpr float kPScale8 = 256.f;            // P is scaled up before it is rounded to f16 (fp8 path)
+
+template <int NW, int NS, int MAXD, bool FP8 = false>
 struct DecodeSmem {
-  static constexpr int kStageBytes = NW * NS * kPageBytes;
-  static constexpr int kBarOff = kStageBytes;
+  static constexpr int kSlice = FP8 ? kPageBytes8 : kPageBytes;
+  static constexpr int kStageBytes = NW * NS * kSlice;
+  static constexpr int kScaleOff = kStageBytes;                      // fp8: NW * NS x 128 bytes of scales
+  static constexpr int kBarOff = kScaleOff + (FP8 ? NW * NS * kScaleBytes8 : 0);
   static constexpr int kROff = kBarOff + NW * NS * 8;
   static constexpr int kFlatOff = kROff + MAXD * 4;
   static constexpr int kQposOff = kFlatOff + MAXD * 4;
@@ -305,10 +313,18 @@ gather_wait_all_kernel(const unsigned* __restrict__ flags, const unsigned* __res
 
 // HEADS = local kv heads served by the launch (1, 2, 4 or 8); the CTA's NW warps form SUB = NW / HEADS
 // groups of HEADS warps, and group `sub` of CTA b owns segment b * SUB + sub of the flat page list.
-template <int NW, int NS, int HEADS, int MINB, int MAXD>
+// FP8: the cache holds e4m3 bytes with one fp32 scale per (token, head, plane). A page slice is 4 KiB
+// (+ 128 bytes of scales, a second copy on the same barrier). K and V are widened to f16 in registers
+// (exact) and the products run as f16 MMAs; the K scale multiplies the score column, the V scale the
+// probability, so no element is ever multiplied by its scale one at a time. The contraction over the
+// 128 dims and the order of the output dims are permuted so that every lane fetches 16 contiguous
+// bytes: lane (g, t) reads dims [32t, 32t+32) of its two key tokens for Q K^T, and dims [16g, 16g+16) of
+// its four value tokens for P V, whose accumulator columns then hold dims 32t+j and 32t+16+j.
+template <int NW, int NS, int HEADS, int MINB, int MAXD, bool FP8 = false>
 __global__ void __launch_bounds__(NW * 32, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
-  using L = DecodeSmem<NW, NS, MAXD>;
+  using L = DecodeSmem<NW, NS, MAXD, FP8>;
+  constexpr int kSlice = L::kSlice;
   constexpr int SUB = NW / HEADS;
   static_assert(NW % HEADS == 0, "warps must divide evenly over the heads");
   extern __shared__ uint8_t smem_raw[];
@@ -406,7 +422,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   unsigned long long* counters =
       reinterpret_cast<unsigned long long*>(P.pl + decode_counter_base(P.partial_slots, n_decode * P.n_kv));
 
-  uint8_t* my_stage = smem + warp * NS * kPageBytes;
+  uint8_t* my_stage = smem + warp * NS * kSlice;
+  uint8_t* my_scale = smem + L::kScaleOff + warp * NS * kScaleBytes8;  // fp8 only
   uint64_t* my_bar = bars + warp * NS;
   bool dead = false;  // a wait ran out: stop waiting, finish the control flow, status is set
 
@@ -431,8 +448,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     if (static_cast<unsigned>(p_blk) >= static_cast<unsigned>(P.num_blocks))
       report(FQB_ERR_INDEX, kKidDecode, p_blk);  // the load below then reads zeros
     if (lane == 0) {
-      mbar_expect_tx(&my_bar[islot], kPageBytes);
-      tma_load_page(my_stage + islot * kPageBytes, &tmap, &my_bar[islot], 0, 0, kvh * 2, 0, p_blk);
+      if constexpr (FP8) {
+        const bool ok = static_cast<unsigned>(p_blk) < static_cast<unsigned>(P.num_blocks);
+        mbar_expect_tx(&my_bar[islot], kPageBytes8 + kScaleBytes8);
+        tma_load_page(my_stage + islot * kPageBytes8, &tmap, &my_bar[islot], 0, 0, kvh, 0, p_blk);
+        bulk_load(my_scale + islot * kScaleBytes8,
+                  P.scales + (static_cast<long long>(ok ? p_blk : 0) * P.n_kv + kvh) * (2 * kTok), kScaleBytes8,
+                  &my_bar[islot]);
+      } else {
+        mbar_expect_tx(&my_bar[islot], kPageBytes);
+        tma_load_page(my_stage + islot * kPageBytes, &tmap, &my_bar[islot], 0, 0, kvh * 2, 0, p_blk);
+      }
     }
     islot = (islot + 1 == NS) ? 0 : islot + 1;
     p_page += 1;
@@ -489,19 +515,39 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     }
   };
 
+  // fp8 path: lane (g, t) holds q dims [32t, 32t+32) of head g as f16 pairs, two words per k-step
+  auto load_q8 = [&](uint32_t (&dst)[8][2], int di) {
+    const uint4* qv = reinterpret_cast<const uint4*>(
+        P.q + static_cast<long long>(s_flat[di]) * P.q_stride + kvh * (kGroup * kHd) + (g & 3) * kHd + 32 * t);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // 8 bf16 = k-steps 2c and 2c+1
+      const uint4 v = __ldg(qv + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo_f = __uint_as_float(w[i] << 16), hi_f = __uint_as_float(w[i] & 0xffff0000u);
+        const uint32_t h = pack_f16(lo_f, hi_f);
+        dst[2 * c + (i >> 1)][i & 1] = g < kGroup ? h : 0u;
+      }
+    }
+  };
+  auto fetch_q = [&](uint32_t (&dst)[8][2], int di) {
+    if constexpr (FP8) load_q8(dst, di); else load_q(dst, di);
+  };
+
   ItemCursor cc;
   item_at(cc, lo, hi, n_decode, s_cum);
   int cslot = 0;
   uint32_t cphase = 0;
   uint32_t qa[8][2], qn[8][2];
-  if (cc.off < hi) load_q(qa, cc.di);
+  if (cc.off < hi) fetch_q(qa, cc.di);
   const long long plane_elems = static_cast<long long>(kTok) * P.n_kv * kHd;
 
 #pragma unroll 1
   while (cc.off < hi) {
     ItemCursor nx;
     item_at(nx, cc.off + (cc.pe - cc.pb), hi, n_decode, s_cum);
-    if (nx.off < hi) load_q(qn, nx.di);  // lands while this item is processed
+    if (nx.off < hi) fetch_q(qn, nx.di);  // lands while this item is processed
 
     float o[16][4];
 #pragma unroll
@@ -525,65 +571,144 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
         dead = true;
         report(FQB_ERR_TIMEOUT, kKidDecode, page);
       }
-      uint8_t* st = my_stage + cslot * kPageBytes;
+      uint8_t* st = my_stage + cslot * kSlice;
       const int nvalid = min(kTok, qpos - page * kTok + 1);
-      if (appends) {
-        const int slot = qpos & (kTok - 1), plane = lane >> 4;
-        if (static_cast<unsigned>(a_blk) < static_cast<unsigned>(P.num_blocks))
-          *reinterpret_cast<uint4*>(P.cache_w + (static_cast<long long>(a_blk) * FQB_PLANES + plane) * plane_elems +
-                                    static_cast<long long>(slot) * (P.n_kv * kHd) + kvh * kHd + (lane & 15) * 8) = new_row;
-        *reinterpret_cast<uint4*>(st + plane * kPlaneBytes + page_chunk_off(slot, lane & 15)) = new_row;
-      }
-      if (nvalid < kTok) {
-        // tail of the sequence's last page was never written: its V rows may hold anything
-        if (lane < 16)
+      if constexpr (!FP8) {
+        if (appends) {
+          const int slot = qpos & (kTok - 1), plane = lane >> 4;
+          if (static_cast<unsigned>(a_blk) < static_cast<unsigned>(P.num_blocks))
+            *reinterpret_cast<uint4*>(P.cache_w + (static_cast<long long>(a_blk) * FQB_PLANES + plane) * plane_elems +
+                                      static_cast<long long>(slot) * (P.n_kv * kHd) + kvh * kHd + (lane & 15) * 8) = new_row;
+          *reinterpret_cast<uint4*>(st + plane * kPlaneBytes + page_chunk_off(slot, lane & 15)) = new_row;
+        }
+        if (nvalid < kTok) {
+          // tail of the sequence's last page was never written: its V rows may hold anything
+          if (lane < 16)
+            for (int row = nvalid; row < kTok; ++row)
+              *reinterpret_cast<uint4*>(st + kPlaneBytes + (lane >> 3) * kHalfBytes + row * 128 +
+                                        ((lane & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        if (appends || nvalid < kTok) {
+          // generic-proxy writes into a buffer the async proxy (TMA) refills later
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+        }
+        const uint32_t kbase = smem_u32(st), vbase = kbase + kPlaneBytes;
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(kbase + page_chunk_off(k_tok, ks * 2 + k_sel), b0, b1, b2, b3);
+          mma_bf16(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+          mma_bf16(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+        float x00 = s0[0] * P.scale_log2, x01 = s0[1] * P.scale_log2;
+        float x10 = s1[0] * P.scale_log2, x11 = s1[1] * P.scale_log2;
+        if (nvalid < kTok) {
+          if (2 * t >= nvalid) x00 = kNegBig;
+          if (2 * t + 1 >= nvalid) x01 = kNegBig;
+          if (2 * t + 8 >= nvalid) x10 = kNegBig;
+          if (2 * t + 9 >= nvalid) x11 = kNegBig;
+        }
+        float mx = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mnew = fmaxf(m, mx);
+        const float corr = fast_exp2(m - mnew);
+        m = mnew;
+        const float p00 = fast_exp2(x00 - mnew), p01 = fast_exp2(x01 - mnew);
+        const float p10 = fast_exp2(x10 - mnew), p11 = fast_exp2(x11 - mnew);
+        l = l * corr + ((p00 + p01) + (p10 + p11));
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          o[j][0] *= corr;
+          o[j][1] *= corr;
+        }
+        const uint32_t pa0 = pack_bf16(p00, p01), pa2 = pack_bf16(p10, p11);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_trans(vbase + page_chunk_off(v_tok, jj * 2 + v_sel), b0, b1, b2, b3);
+          mma_bf16(o[2 * jj], pa0, 0u, pa2, 0u, b0, b1);
+          mma_bf16(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+      } else {
+        if (nvalid < kTok) {
+          // tail of the sequence's last page was never written: bytes there may decode to NaN
           for (int row = nvalid; row < kTok; ++row)
-            *reinterpret_cast<uint4*>(st + kPlaneBytes + (lane >> 3) * kHalfBytes + row * 128 +
-                                      ((lane & 7) << 4)) = make_uint4(0, 0, 0, 0);
-      }
-      if (appends || nvalid < kTok) {
-        // generic-proxy writes into a buffer the async proxy (TMA) refills later
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-      }
-      const uint32_t kbase = smem_u32(st), vbase = kbase + kPlaneBytes;
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            if (lane < 8) *reinterpret_cast<uint4*>(st + kPageBytes8 / 2 + row * 128 + (lane << 4)) = make_uint4(0, 0, 0, 0);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+        }
+        const float* sc = reinterpret_cast<const float*>(my_scale + cslot * kScaleBytes8);
+        const uint32_t kbase = smem_u32(st), vbase = kbase + kPageBytes8 / 2;
+        // ---- S = Q K^T: key tokens g (tile 0) and g + 8 (tile 1), this lane's 32 dims of each ----
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          uint32_t kw[2][8];
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4(kbase + page_chunk_off(k_tok, ks * 2 + k_sel), b0, b1, b2, b3);
-        mma_bf16(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-        mma_bf16(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
-      }
-      float x00 = s0[0] * P.scale_log2, x01 = s0[1] * P.scale_log2;
-      float x10 = s1[0] * P.scale_log2, x11 = s1[1] * P.scale_log2;
-      if (nvalid < kTok) {
-        if (2 * t >= nvalid) x00 = kNegBig;
-        if (2 * t + 1 >= nvalid) x01 = kNegBig;
-        if (2 * t + 8 >= nvalid) x10 = kNegBig;
-        if (2 * t + 9 >= nvalid) x11 = kNegBig;
-      }
-      float mx = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float mnew = fmaxf(m, mx);
-      const float corr = fast_exp2(m - mnew);
-      m = mnew;
-      const float p00 = fast_exp2(x00 - mnew), p01 = fast_exp2(x01 - mnew);
-      const float p10 = fast_exp2(x10 - mnew), p11 = fast_exp2(x11 - mnew);
-      l = l * corr + ((p00 + p01) + (p10 + p11));
+          for (int tile = 0; tile < 2; ++tile) {
+            const int tok = g + 8 * tile;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        o[j][0] *= corr;
-        o[j][1] *= corr;
-      }
-      const uint32_t pa0 = pack_bf16(p00, p01), pa2 = pack_bf16(p10, p11);
+            for (int c = 0; c < 2; ++c) {
+              uint32_t x0, x1, x2, x3;
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                           : "r"(kbase + tok * 128 + (((2 * t + c) ^ (tok & 7)) << 4)));
+              kw[tile][4 * c] = x0; kw[tile][4 * c + 1] = x1; kw[tile][4 * c + 2] = x2; kw[tile][4 * c + 3] = x3;
+            }
+          }
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_trans(vbase + page_chunk_off(v_tok, jj * 2 + v_sel), b0, b1, b2, b3);
-        mma_bf16(o[2 * jj], pa0, 0u, pa2, 0u, b0, b1);
-        mma_bf16(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);
+          for (int ks = 0; ks < 8; ++ks) {
+            mma_f16(s0, qa[ks][0], 0u, qa[ks][1], 0u, e4m3x2_to_f16x2(kw[0][ks]), e4m3x2_to_f16x2(kw[0][ks] >> 16));
+            mma_f16(s1, qa[ks][0], 0u, qa[ks][1], 0u, e4m3x2_to_f16x2(kw[1][ks]), e4m3x2_to_f16x2(kw[1][ks] >> 16));
+          }
+        }
+        const float2 ka = *reinterpret_cast<const float2*>(sc + 2 * t), kb = *reinterpret_cast<const float2*>(sc + 8 + 2 * t);
+        float2 va = *reinterpret_cast<const float2*>(sc + kTok + 2 * t), vb = *reinterpret_cast<const float2*>(sc + kTok + 8 + 2 * t);
+        float x00 = s0[0] * (ka.x * P.scale_log2), x01 = s0[1] * (ka.y * P.scale_log2);
+        float x10 = s1[0] * (kb.x * P.scale_log2), x11 = s1[1] * (kb.y * P.scale_log2);
+        if (nvalid < kTok) {  // scores and value scales of slots that were never written are not trusted
+          if (2 * t >= nvalid) { x00 = kNegBig; va.x = 0.f; }
+          if (2 * t + 1 >= nvalid) { x01 = kNegBig; va.y = 0.f; }
+          if (2 * t + 8 >= nvalid) { x10 = kNegBig; vb.x = 0.f; }
+          if (2 * t + 9 >= nvalid) { x11 = kNegBig; vb.y = 0.f; }
+        }
+        float mx = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mnew = fmaxf(m, mx);
+        const float corr = fast_exp2(m - mnew);
+        m = mnew;
+        const float p00 = fast_exp2(x00 - mnew), p01 = fast_exp2(x01 - mnew);
+        const float p10 = fast_exp2(x10 - mnew), p11 = fast_exp2(x11 - mnew);
+        l = l * corr + ((p00 + p01) + (p10 + p11));
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          o[j][0] *= corr;
+          o[j][1] *= corr;
+        }
+        const uint32_t pa0 = pack_f16(p00 * (va.x * kPScale8), p01 * (va.y * kPScale8));
+        const uint32_t pa2 = pack_f16(p10 * (vb.x * kPScale8), p11 * (vb.y * kPScale8));
+        // ---- O += P V: value tokens 2t, 2t+1, 2t+8, 2t+9, dims 16g .. 16g+15 (accumulator tile j = dim 16g+j) ----
+        uint32_t vr[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(vr[i][0]), "=r"(vr[i][1]), "=r"(vr[i][2]), "=r"(vr[i][3])
+                       : "r"(vbase + tok * 128 + ((g ^ (tok & 7)) << 4)));
+        }
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          // bytes (j, j+1) of rows 0/1 interleaved, then (j+2, j+3): two key pairs per permute
+          const uint32_t e01a = __byte_perm(vr[0][wd], vr[1][wd], 0x5140), e01b = __byte_perm(vr[0][wd], vr[1][wd], 0x7362);
+          const uint32_t e23a = __byte_perm(vr[2][wd], vr[3][wd], 0x5140), e23b = __byte_perm(vr[2][wd], vr[3][wd], 0x7362);
+          mma_f16(o[4 * wd + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01a), e4m3x2_to_f16x2(e23a));
+          mma_f16(o[4 * wd + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01a >> 16), e4m3x2_to_f16x2(e23a >> 16));
+          mma_f16(o[4 * wd + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01b), e4m3x2_to_f16x2(e23b));
+          mma_f16(o[4 * wd + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01b >> 16), e4m3x2_to_f16x2(e23b >> 16));
+        }
       }
       __syncwarp();  // every lane has read the buffer before it is refilled
       cslot = (cslot + 1 == NS) ? 0 : cslot + 1;
@@ -595,32 +720,74 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     const bool whole = cc.pb == 0 && cc.pe == cc.np;
+    if constexpr (FP8) {  // P carried a factor of kPScale8
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        o[j][0] *= 1.f / kPScale8;
+        o[j][1] *= 1.f / kPScale8;
+      }
+    }
+    const int b0 = whole ? 0 : s_cum[cc.di] / W, b1 = whole ? 0 : (s_cum[cc.di] + cc.np - 1) / W;  // segments that see this sequence
+    unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
     if (whole) {
       // the pair lies inside this segment: straight from registers to `out`
       if (g < kGroup) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        uint32_t w[16];
+        if constexpr (!FP8) {
+          uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(
-            P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
+          for (int j = 0; j < 16; ++j) w[j] = pack_bf16(o[j][0] * inv, o[j][1] * inv);
+          uint32_t* dst = reinterpret_cast<uint32_t*>(
+              P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j * 4 + t] = w[j];
-        for (int r = 0; r < P.n_peers; ++r) {
-          uint32_t* pd = reinterpret_cast<uint32_t*>(
-              P.peer_out[r] + (static_cast<long long>(flat) * P.peer_heads + P.peer_col + kvh * kGroup + g) * kHd);
+          for (int j = 0; j < 16; ++j) dst[j * 4 + t] = w[j];
+          for (int r = 0; r < P.n_peers; ++r) {
+            uint32_t* pd = reinterpret_cast<uint32_t*>(
+                P.peer_out[r] + (static_cast<long long>(flat) * P.peer_heads + P.peer_col + kvh * kGroup + g) * kHd);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) pd[j * 4 + t] = w[j];
+            for (int j = 0; j < 16; ++j) pd[j * 4 + t] = w[j];
+          }
+        } else {
+          // accumulator tile j holds dims 32t + j (column 0) and 32t + 16 + j (column 1): 32 contiguous dims
+          uint4 w[4];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            w[2 * c].x = pack_bf16(o[0][c] * inv, o[1][c] * inv);
+            w[2 * c].y = pack_bf16(o[2][c] * inv, o[3][c] * inv);
+            w[2 * c].z = pack_bf16(o[4][c] * inv, o[5][c] * inv);
+            w[2 * c].w = pack_bf16(o[6][c] * inv, o[7][c] * inv);
+            w[2 * c + 1].x = pack_bf16(o[8][c] * inv, o[9][c] * inv);
+            w[2 * c + 1].y = pack_bf16(o[10][c] * inv, o[11][c] * inv);
+            w[2 * c + 1].z = pack_bf16(o[12][c] * inv, o[13][c] * inv);
+            w[2 * c + 1].w = pack_bf16(o[14][c] * inv, o[15][c] * inv);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(
+              P.out + (static_cast<long long>(flat) * P.n_heads + kvh * kGroup + g) * kHd + 32 * t);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = w[i];
+          for (int r = 0; r < P.n_peers; ++r) {
+            uint4* pd = reinterpret_cast<uint4*>(
+                P.peer_out[r] + (static_cast<long long>(flat) * P.peer_heads + P.peer_col + kvh * kGroup + g) * kHd + 32 * t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pd[i] = w[i];
+          }
         }
       }
     } else {
-      const int b0 = s_cum[cc.di] / W, b1 = (s_cum[cc.di] + cc.np - 1) / W;  // segments that see this sequence
-      unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
       const long long slot0 = ((static_cast<long long>(cc.di) + seg) * P.n_kv + kvh) * kGroup;
       if (g < kGroup) {
-        float* dst = P.pa + (slot0 + g) * kHd + 2 * t;
+        if constexpr (!FP8) {
+          float* dst = P.pa + (slot0 + g) * kHd + 2 * t;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
+          for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0], o[j][1]);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(P.pa + (slot0 + g) * kHd + 32 * t);
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[4 * c + i] = make_float4(o[4 * i][c], o[4 * i + 1][c], o[4 * i + 2][c], o[4 * i + 3][c]);
+        }
         if (t == 0) {
           P.pm[slot0 + g] = m;
           P.pl[slot0 + g] = l;

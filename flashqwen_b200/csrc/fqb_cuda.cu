@@ -119,6 +119,47 @@ int make_cache_map(const void* cache, int num_blocks, int kv_heads_local, CUtens
   return FQB_OK;
 }
 
+// fp8 cache [num_blocks][2][16][kv_heads*128] bytes as a 5-D tensor of bytes:
+//   d0 = 128 bytes of one head, d1 = 16 tokens, d2 = heads, d3 = 2 planes, d4 = blocks.
+// One box {128,16,1,2,1} is the K and V slice of one kv head of one page (4 KiB), rows of 128 bytes,
+// 128-byte swizzle.
+int make_cache_map_fp8(const void* cache8, int num_blocks, int kv_heads_local, CUtensorMap& map) {
+  struct Entry {
+    const void* ptr;
+    int nb, kvh;
+    CUtensorMap map;
+  };
+  constexpr int kCache = 64;
+  static thread_local Entry lru[kCache];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i)
+    if (lru[i].ptr == cache8 && lru[i].nb == num_blocks && lru[i].kvh == kv_heads_local) {
+      map = lru[i].map;
+      return FQB_OK;
+    }
+  EncodeFn enc;
+  if (int rc = get_encode(enc)) return rc;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(kv_heads_local) * kHd;
+  cuuint64_t dims[5] = {static_cast<cuuint64_t>(kHd), static_cast<cuuint64_t>(kTok), static_cast<cuuint64_t>(kv_heads_local),
+                        2, static_cast<cuuint64_t>(num_blocks)};
+  cuuint64_t strides[4] = {row_bytes, static_cast<cuuint64_t>(kHd), row_bytes * kTok, row_bytes * kTok * 2};
+  cuuint32_t box[5] = {static_cast<cuuint32_t>(kHd), static_cast<cuuint32_t>(kTok), 1, 2, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(cache8), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(FQB_ERR_CUDA, "cuTensorMapEncodeTiled (fp8 cache) failed with CUresult %d", static_cast<int>(r));
+  Entry& e = lru[next];
+  e.ptr = cache8;
+  e.nb = num_blocks;
+  e.kvh = kv_heads_local;
+  e.map = map;
+  next = (next + 1) % kCache;
+  if (used < kCache) ++used;
+  return FQB_OK;
+}
+
 int check_attn_shape(int n_heads, int n_kv, int head_dim, int block_size) {
   if (head_dim != kHd) return set_error(FQB_ERR_SHAPE, "head_dim %d: only 128 is supported", head_dim);
   if (block_size != kTok) return set_error(FQB_ERR_SHAPE, "block_size %d: only 16 is supported", block_size);
@@ -139,6 +180,11 @@ using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
+// fp8 cache: slices are half the size, so the rings are twice as deep for the same bytes in flight
+using Decode8Cfg8 = DecodeCfg<8, 6, 8, 1, 512>;
+using Decode8Cfg4 = DecodeCfg<4, 6, 4, 2, 256>;
+using Decode8Cfg2 = DecodeCfg<4, 6, 2, 2, 256>;
+using Decode8Cfg1 = DecodeCfg<4, 6, 1, 2, 256>;
 
 // CTAs per SM of a default-mode launch of the 4-, 2- and 1-head shapes (build-time choice; measured on
 // B200 with every launch waiting for the one before it: 1 beats 2 for the 4-head and the 1-head shape).
@@ -240,11 +286,11 @@ int launch_prefill(int max_qlen, int n_kv, int R, const CUtensorMap& map, const 
 
 // ctas_per_sm: how many CTAs of THIS launch go on each SM (the kernel may allow more to be resident,
 // so that the CTAs of the launch after it can move in beside them).
-template <class Cfg>
+template <class Cfg, bool FP8 = false>
 int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n_decode, int sm_count,
                   int ctas_per_sm, bool pdl, cudaStream_t st) {
-  using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD>;
-  auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD>;
+  using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD, FP8>;
+  auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD, FP8>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
@@ -358,6 +404,51 @@ int64_t fqb_attn_decode_partial_slots(int max_decode, int n_heads_local, int max
   return regions * one;
 }
 
+static int decode_impl(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
+                       int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                       const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
+                       float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
+                       const int32_t* plan, void* cache_w, long long k_rel, long long v_rel, const fqb_gather* gather,
+                       const float* scales, void* stream);
+
+int64_t fqb_kv_pool_bytes_fp8(int num_blocks, int kv_heads_local) {
+  if (num_blocks <= 0 || kv_heads_local <= 0) return 0;
+  return static_cast<int64_t>(num_blocks) * FQB_PLANES * kTok * kv_heads_local * kHd;
+}
+int64_t fqb_kv_scale_bytes_fp8(int num_blocks, int kv_heads_local) {
+  if (num_blocks <= 0 || kv_heads_local <= 0) return 0;
+  return static_cast<int64_t>(num_blocks) * kv_heads_local * FQB_PLANES * kTok * 4;
+}
+
+int fqb_kv_append_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                      int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row, const int32_t* pos,
+                      int M, void* stream) {
+  if (M <= 0) return FQB_OK;
+  if (!cache8 || !scales || !qkv || !bt || !bt_row || !pos) return set_error(FQB_ERR_INVALID, "kv_append_fp8: null pointer");
+  if (num_blocks <= 0 || kv_heads_local <= 0 || bt_stride <= 0)
+    return set_error(FQB_ERR_INVALID, "kv_append_fp8: non-positive size");
+  if (!aligned16(cache8) || !aligned16(scales) || !aligned16(qkv) || (src_stride % 8) || (k_off % 8) || (v_off % 8))
+    return set_error(FQB_ERR_INVALID, "kv_append_fp8: pointers, src_stride, k_off and v_off must keep 16-byte alignment");
+  AppendParams P{static_cast<__nv_bfloat16*>(cache8), num_blocks, kv_heads_local * kHd,
+                 static_cast<const __nv_bfloat16*>(qkv), src_stride, k_off, v_off, bt, bt_stride, bt_row, pos, M};
+  FQB_CUDA_TRY(launch_ex(kv_append_fp8_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), true, P, scales));
+  return FQB_OK;
+}
+
+int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const float* scales, int num_blocks, void* out,
+                        int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
+                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
+                        void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (!scales) return set_error(FQB_ERR_INVALID, "attn_decode_fp8: null pointer");
+  if (flags & FQB_DECODE_HISTORY_STABLE)
+    return set_error(FQB_ERR_INVALID, "attn_decode_fp8: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode");
+  return decode_impl(q, q_stride, cache8, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
+                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, nullptr,
+                     scales, stream);
+}
+
 int64_t fqb_attn_decode_slots_needed(int n_decode, int n_kv) {
   if (n_decode <= 0 || n_kv <= 0) return 0;
   DeviceInfo di;
@@ -386,8 +477,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
                        const int32_t* plan, void* cache_w, long long k_rel, long long v_rel, const fqb_gather* gather,
-                       void* stream) {
+                       const float* scales, void* stream) {
   if (n_decode <= 0 && !gather) return FQB_OK;
+  const bool fp8 = scales != nullptr;
   if (plan && (n_decode > 256 || (reinterpret_cast<uintptr_t>(plan) & 15u)))
     return set_error(FQB_ERR_INVALID, "attn_decode: a step plan serves at most 256 sequences per call and must be 16-byte aligned");
   if (int rc = check_attn_shape(n_heads, n_kv, head_dim, block_size)) return rc;
@@ -405,13 +497,16 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   DeviceInfo di;
   if (int rc = device_info(di)) return rc;
   CUtensorMap map;
-  if (int rc = make_cache_map(cache, num_blocks, n_kv, map)) return rc;
+  if (int rc = fp8 ? make_cache_map_fp8(cache, num_blocks, n_kv, map) : make_cache_map(cache, num_blocks, n_kv, map)) return rc;
+  if (fp8 && (!aligned16(scales) || (q_stride % 8)))
+    return set_error(FQB_ERR_INVALID, "attn_decode_fp8: scales and q rows must keep 16-byte alignment");
   DecodeParams P;
   P.q = static_cast<const __nv_bfloat16*>(q);
   P.q_stride = q_stride;
   P.out = static_cast<__nv_bfloat16*>(out);
   P.n_heads = n_heads;
   P.n_kv = n_kv;
+  P.scales = scales;
   P.pos = pos;
   P.qstart = qstart;
   P.rids = decode_rids;
@@ -478,9 +573,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
         const int left = n_kv - base;
         P.kvh_base = base;
         int rc, took;
-        if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
-        else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        if (left >= 4) { rc = fp8 ? launch_decode<Decode8Cfg4, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
+        else if (left >= 2) { rc = fp8 ? launch_decode<Decode8Cfg2, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
+        else { rc = fp8 ? launch_decode<Decode8Cfg1, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
         P.sync_first = 0;  // later launches of the call serve other heads: disjoint partials and counters
@@ -502,10 +597,10 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     const int left = n_kv - base;
     P.kvh_base = base;
     int rc, took;
-    if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
-    else if (left >= 4) { rc = launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
-    else if (left >= 2) { rc = launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
-    else { rc = launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
+    if (left >= 8) { rc = fp8 ? launch_decode<Decode8Cfg8, true>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st) : launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
+    else if (left >= 4) { rc = fp8 ? launch_decode<Decode8Cfg4, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
+    else if (left >= 2) { rc = fp8 ? launch_decode<Decode8Cfg2, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
+    else { rc = fp8 ? launch_decode<Decode8Cfg1, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
     if (rc != FQB_OK) return rc;
     base += took;
     P.mode = kDecodeWaitFirst;
@@ -522,7 +617,7 @@ int fqb_attn_decode_ex(const void* q, int q_stride, const void* cache, int num_b
     return set_error(FQB_ERR_INVALID, "attn_decode: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode "
                                       "(a separate append kernel in front writes the cache this call reads)");
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids, n_decode,
-                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, nullptr, stream);
+                     bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, nullptr, nullptr, 0, 0, nullptr, nullptr, stream);
 }
 
 int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -534,7 +629,7 @@ int fqb_attn_decode_planned(const void* q, int q_stride, const void* cache, int 
     return set_error(FQB_ERR_INVALID, "attn_decode_planned: FQB_DECODE_HISTORY_STABLE belongs to fqb_append_attn_decode");
   // pos / qstart / decode_rids are not read when a plan is given; the plan pointer stands in for them
   return decode_impl(q, q_stride, cache, num_blocks, out, n_heads, n_kv, head_dim, plan, plan, plan, n_decode, bt,
-                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, nullptr, 0, 0, nullptr, stream);
+                     max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, nullptr, 0, 0, nullptr, nullptr, stream);
 }
 
 int fqb_attn_decode(const void* q, int q_stride, const void* cache, int num_blocks, void* out, int n_heads,
@@ -562,7 +657,7 @@ static int append_decode(void* cache, int num_blocks, int kv_heads_local, const 
   const int32_t* m2 = plan ? plan : decode_rids;
   return decode_impl(q, src_stride, cache, num_blocks, out, kv_heads_local * kGroup, kv_heads_local, head_dim, m0, m1, m2,
                      n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, cache,
-                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, gather, stream);
+                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, gather, nullptr, stream);
 }
 
 int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,

@@ -6,6 +6,8 @@
 // CTA takes one token row, looks its page up once, and moves the row with 16-byte loads/stores.
 #pragma once
 
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace fqb {
@@ -56,6 +58,42 @@ kv_append_kernel(const AppendParams P) {
     const int i = v - pl * vecs;
     const uint4 val = __ldg(reinterpret_cast<const uint4*>(src + (pl ? P.v_off : P.k_off)) + i);
     *(reinterpret_cast<uint4*>(P.cache + dst + pl * plane) + i) = val;
+  }
+}
+
+// fp8 form of the append: each head's 128 K (and V) values are stored as e4m3 bytes with one fp32
+// scale per (token, head, plane): s = amax / 448 (1 for an all-zero row), byte = e4m3(x * (448 / amax))
+// rounded to nearest even, saturating. cache is [num_blocks][2][16][row_elems] BYTES (P.cache is used
+// as a byte pointer), scales [num_blocks][heads][2][16] fp32. One warp per (plane, head); every step is
+// one IEEE operation, so the host restatement gives the same bytes.
+__global__ void __launch_bounds__(256)
+kv_append_fp8_kernel(const AppendParams P, float* __restrict__ scales) {
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
+  long long dst;  // element offset of the token slot in the K plane; elements are bytes here
+  if (!append_dst(P, m, kKidAppend, dst)) return;
+  const int heads = P.row_elems / kHd;
+  const int p = P.pos[m];
+  const long long blk = dst / (static_cast<long long>(FQB_PLANES) * kTok * P.row_elems);
+  const long long plane = static_cast<long long>(kTok) * P.row_elems;
+  uint8_t* cache8 = reinterpret_cast<uint8_t*>(P.cache);
+  const __nv_bfloat16* src = P.qkv + static_cast<long long>(m) * P.src_stride;
+  for (int hd = warp; hd < 2 * heads; hd += 8) {
+    const int pl = hd >= heads, h = hd - pl * heads;
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + (pl ? P.v_off : P.k_off) + h * kHd) + lane);
+    const float x0 = __uint_as_float(raw.x << 16), x1 = __uint_as_float(raw.x & 0xffff0000u);
+    const float x2 = __uint_as_float(raw.y << 16), x3 = __uint_as_float(raw.y & 0xffff0000u);
+    float amax = fmaxf(fmaxf(fabsf(x0), fabsf(x1)), fmaxf(fabsf(x2), fabsf(x3)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+    const float inv = amax > 0.f ? __fdiv_rn(448.0f, amax) : 0.0f;
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x0, inv), __fmul_rn(x1, inv)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x2, inv), __fmul_rn(x3, inv)), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint32_t*>(cache8 + dst + pl * plane + h * kHd + 4 * lane) = lo | (hi << 16);
+    if (lane == 0) scales[((blk * heads + h) * 2 + pl) * kTok + p % kTok] = s;
   }
 }
 

@@ -119,6 +119,23 @@ def gather_wait_all(gather, stream=None):
     check(lib.fqb_gather_wait_all(C.addressof(gather), _stream(stream)), "fqb_gather_wait_all")
 
 
+def kv_append_fp8(cache8, scales, num_blocks, kv_heads_local, qkv, src_stride, k_off, v_off, bt, bt_stride, bt_row, pos,
+                  M, stream=None):
+    """fqb_kv_append_fp8: the append with per-(token, head, plane) e4m3 quantisation."""
+    check(lib.fqb_kv_append_fp8(_ptr(cache8), _ptr(scales), num_blocks, kv_heads_local, _ptr(qkv), src_stride, k_off,
+                                v_off, _ptr(bt), bt_stride, _ptr(bt_row), _ptr(pos), M, _stream(stream)),
+          "fqb_kv_append_fp8")
+
+
+def attn_decode_fp8(q, q_stride, cache8, scales, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
+                    n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, stream=None, flags=0):
+    """fqb_attn_decode_fp8: decode attention over the e4m3 cache."""
+    check(lib.fqb_attn_decode_fp8(_ptr(q), q_stride, _ptr(cache8), _ptr(scales), num_blocks, _ptr(out), n_heads, n_kv,
+                                  head_dim, _ptr(pos), _ptr(qstart), _ptr(decode_rids), n_decode, _ptr(bt), max_blocks,
+                                  block_size, scale, _ptr(pm), _ptr(pl), _ptr(pa), partial_slots, flags,
+                                  _stream(stream)), "fqb_attn_decode_fp8")
+
+
 def attn_decode_static(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                        n_decode, bt, max_blocks, block_size, scale, stream=None):
     """fqb_attn_decode_static: decode attention with the library's built-in scratch, for callers that

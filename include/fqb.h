@@ -181,6 +181,29 @@ int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, cons
                            const int32_t* bt, int max_blocks, int block_size, float scale, float* pm, float* pl,
                            float* pa, int64_t partial_slots, unsigned flags, void* stream);
 
+/* ---- fp8 (e4m3) KV cache: kernels 1 and 2 over half the bytes ------------------------------------
+ * No reference counterpart: the reference names an fp8 KV cache as its next lever and has none
+ * (docs/optimization.md:119-120); the format is defined here. cache8 is
+ * [num_blocks][2][16][kv_heads_local*128] e4m3 bytes and scales [num_blocks][kv_heads_local][2][16] fp32:
+ * one scale per (token, kv head, plane), s = amax / 448 over the head's 128 values (1 for an all-zero
+ * row); a stored byte is e4m3(x * (448 / amax)), round to nearest even, saturating; a value reads back
+ * as e4m3_to_float(byte) * s. fqb_kv_append_fp8 quantises the rows as fqb_kv_append copies them (same
+ * arguments); the bytes and scales are reproducible bit for bit on the host. fqb_attn_decode_fp8 is
+ * fqb_attn_decode_ex over that cache: K and V are widened to f16 in registers (exact), the K scale
+ * multiplies the score, the V scale the probability; flags 0 or FQB_DECODE_INDEPENDENT. Against the
+ * exact softmax over the DEQUANTISED cache the outputs agree to the same 2e-2 as the bf16 kernels;
+ * against the bf16 cache they differ by the quantisation itself (about 2^-4 relative per K / V value). */
+int64_t fqb_kv_pool_bytes_fp8(int num_blocks, int kv_heads_local);
+int64_t fqb_kv_scale_bytes_fp8(int num_blocks, int kv_heads_local);
+int fqb_kv_append_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
+                      int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row,
+                      const int32_t* pos, int M, void* stream);
+int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const float* scales, int num_blocks, void* out,
+                        int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
+                        const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,
+                        float scale, float* pm, float* pl, float* pa, int64_t partial_slots, unsigned flags,
+                        void* stream);
+
 /* ---- reassembly of the per-head outputs over G GPUs of one node, inside the decode kernel -----------
  * No reference counterpart (the reference is single-GPU). With the KV heads sharded over G GPUs every
  * rank produces [rows][(32/G)*128]; where full rows are wanted on every GPU, the kernel that finishes a

@@ -89,6 +89,117 @@ void orc_kv_append(uint16_t* cache, int kv_dim, const uint16_t* qkv, int src_str
 }
 
 // ---------------------------------------------------------------------------------------------
+// fp8 KV variant (the reference names fp8 KV as its next lever, docs/optimization.md:119-120, and has
+// no such path; the format is defined here). K and V rows are stored as e4m3 bytes,
+// cache8 [num_blocks][2][16][kv_dim] u8, with one fp32 scale per (token, kv head, plane),
+// scales [num_blocks][n_kv][2][16]: s = amax / 448 over the head's 128 values (s = 1 when the row is
+// all zero), stored byte = e4m3(x * (448 / amax)) rounded to nearest even and saturated to +-448;
+// a value reads back as e4m3_to_float(byte) * s. Every step is a single IEEE fp32 operation, so a
+// device implementation that uses the same operations matches bit for bit.
+// ---------------------------------------------------------------------------------------------
+static inline float e4m3_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v = e == 0 ? std::ldexp(static_cast<float>(m), -9) : std::ldexp(1.0f + m / 8.0f, e - 7);
+  if (e == 15 && m == 7) v = NAN;
+  return (b & 0x80) ? -v : v;
+}
+
+static inline uint8_t f32_to_e4m3(float f) {
+  const uint8_t sign = std::signbit(f) ? 0x80 : 0;
+  float a = std::fabs(f);
+  if (a != a) return sign | 0x7F;
+  if (a >= 464.0f) return sign | 0x7E;  // 464 is halfway to the next step above 448: saturates
+  if (a == 0.0f) return sign;
+  int ex;
+  std::frexp(a, &ex);                   // a = m * 2^ex, m in [0.5, 1): a in [2^(ex-1), 2^ex)
+  int e = ex - 1;
+  if (e < -6) e = -6;                   // subnormals share the quantum of the smallest normal binade
+  const float quantum = std::ldexp(1.0f, e - 3);
+  const float q = std::nearbyint(a / quantum);  // round to nearest even (default rounding mode); exact division
+  const float v = q * quantum;
+  if (v > 448.0f) return sign | 0x7E;
+  if (v < std::ldexp(1.0f, -6)) return sign | static_cast<uint8_t>(q);  // subnormal: q = 0..7
+  int ev;
+  const float mv = std::frexp(v, &ev);  // v = mv * 2^ev, mv in [0.5, 1)
+  const int be = ev - 1 + 7;
+  const int bm = static_cast<int>((mv * 2.0f - 1.0f) * 8.0f);
+  return sign | static_cast<uint8_t>((be << 3) | bm);
+}
+
+uint8_t orc_f32_to_e4m3(float f) { return f32_to_e4m3(f); }
+float orc_e4m3_to_f32(uint8_t b) { return e4m3_to_f32(b); }
+
+void orc_kv_append_fp8(uint8_t* cache8, float* scales, int kv_dim, const uint16_t* qkv, int src_stride,
+                       int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row,
+                       const int32_t* pos, int M) {
+  const int n_kv = kv_dim / kHd;
+  const int64_t plane = static_cast<int64_t>(kTok) * kv_dim;
+  for (int m = 0; m < M; ++m) {
+    const int32_t* row_bt = bt + static_cast<int64_t>(bt_row[m]) * bt_stride;
+    const int p = pos[m];
+    const int64_t blk = row_bt[p / kTok];
+    const uint16_t* src = qkv + static_cast<int64_t>(m) * src_stride;
+    for (int pl = 0; pl < 2; ++pl)
+      for (int h = 0; h < n_kv; ++h) {
+        const uint16_t* x = src + (pl ? v_off : k_off) + h * kHd;
+        float amax = 0.f;
+        for (int d = 0; d < kHd; ++d) amax = std::max(amax, std::fabs(bf2f(x[d])));
+        const float s = amax > 0.f ? amax / 448.0f : 1.0f;
+        const float inv = amax > 0.f ? 448.0f / amax : 0.0f;
+        scales[((blk * n_kv + h) * 2 + pl) * kTok + p % kTok] = s;
+        uint8_t* dst = cache8 + (blk * kPlanes + pl) * plane + static_cast<int64_t>(p % kTok) * kv_dim + h * kHd;
+        for (int d = 0; d < kHd; ++d) dst[d] = f32_to_e4m3(bf2f(x[d]) * inv);
+      }
+  }
+}
+
+// Decode attention over the fp8 cache: orc_attn_decode with every K / V value read back as
+// e4m3_to_float(byte) * scale (exact in fp32: 4 significant bits times a float).
+void orc_attn_decode_fp8(const uint16_t* q, int q_stride, const uint8_t* cache8, const float* scales,
+                         uint16_t* out, int n_heads, int n_kv, const int32_t* pos, const int32_t* qstart,
+                         const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks,
+                         float scale, int nthreads) {
+  const int kv_dim = n_kv * kHd;
+  const int group = n_heads / n_kv;
+  const int64_t plane = static_cast<int64_t>(kTok) * kv_dim;
+  parallel_for(n_decode * n_heads, nthreads, [&](int job) {
+    int di = job / n_heads, h = job % n_heads;
+    int r = decode_rids[di], flat = qstart[r], qpos = pos[flat];
+    int kvh = h / group;
+    const int32_t* row_bt = bt + static_cast<int64_t>(r) * max_blocks;
+    const uint16_t* qv = q + static_cast<int64_t>(flat) * q_stride + static_cast<int64_t>(h) * kHd;
+    float qf[kHd];
+    for (int d = 0; d < kHd; ++d) qf[d] = bf2f(qv[d]);
+    int n = qpos + 1;
+    std::vector<float> s(n > 0 ? n : 0);
+    float mx = -INFINITY;
+    for (int t = 0; t < n; ++t) {
+      const int64_t blk = row_bt[t / kTok];
+      const int64_t base = blk * kPlanes * plane + static_cast<int64_t>(t % kTok) * kv_dim + static_cast<int64_t>(kvh) * kHd;
+      const float ks = scales[((blk * n_kv + kvh) * 2 + 0) * kTok + t % kTok];
+      float dot = 0.f;
+      for (int d = 0; d < kHd; ++d) dot += qf[d] * (e4m3_to_f32(cache8[base + d]) * ks);
+      s[t] = dot * scale;
+      mx = std::max(mx, s[t]);
+    }
+    double acc[kHd];
+    for (int d = 0; d < kHd; ++d) acc[d] = 0.0;
+    double denom = 0.0;
+    for (int t = 0; t < n; ++t) {
+      float p = std::exp(s[t] - mx);
+      denom += p;
+      const int64_t blk = row_bt[t / kTok];
+      const int64_t base = blk * kPlanes * plane + plane + static_cast<int64_t>(t % kTok) * kv_dim + static_cast<int64_t>(kvh) * kHd;
+      const float vs = scales[((blk * n_kv + kvh) * 2 + 1) * kTok + t % kTok];
+      for (int d = 0; d < kHd; ++d) acc[d] += static_cast<double>(p) * (e4m3_to_f32(cache8[base + d]) * vs);
+    }
+    uint16_t* o = out + (static_cast<int64_t>(flat) * n_heads + h) * kHd;
+    for (int d = 0; d < kHd; ++d)
+      o[d] = f2bf(denom > 0.0 ? static_cast<float>(acc[d] / denom) : 0.f);
+  });
+}
+
+// ---------------------------------------------------------------------------------------------
 // Decode attention: engine/src/attn_cute.cu:165-238 (split + combine collapse to one exact
 // softmax). For decode sequence di: r = decode_rids[di], flat = qstart[r], qpos = pos[flat];
 // query head h attends keys 0..qpos inclusive of kv head h / (n_heads / n_kv); the score is

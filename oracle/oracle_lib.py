@@ -75,6 +75,32 @@ def attn_decode(q, q_stride, cache, n_heads, n_kv, pos, qstart, decode_rids, bt,
     return out
 
 
+_pu8 = C.POINTER(C.c_uint8)
+orc.orc_f32_to_e4m3.restype = C.c_uint8
+orc.orc_f32_to_e4m3.argtypes = [C.c_float]
+orc.orc_e4m3_to_f32.restype = C.c_float
+orc.orc_e4m3_to_f32.argtypes = [C.c_uint8]
+
+
+def kv_append_fp8(cache8, scales, qkv, src_stride, k_off, v_off, bt, bt_row, pos):
+    """In place on cache8 ([nb,2,16,kv_dim] uint8) and scales ([nb,n_kv,2,16] float32)."""
+    assert cache8.flags.c_contiguous and cache8.dtype == np.uint8 and scales.flags.c_contiguous and scales.dtype == np.float32
+    kv_dim = cache8.shape[-1]
+    qkv, bt, bt_row, pos = _c(qkv, np.uint16), _c(bt, np.int32), _c(bt_row, np.int32), _c(pos, np.int32)
+    orc.orc_kv_append_fp8(_p(cache8, _pu8), _p(scales, _pf), kv_dim, _p(qkv, _pu16), src_stride, k_off, v_off, _p(bt, _pi),
+                          bt.shape[1], _p(bt_row, _pi), _p(pos, _pi), len(pos))
+
+
+def attn_decode_fp8(q, q_stride, cache8, scales, n_heads, n_kv, pos, qstart, decode_rids, bt, scale, rows, nthreads=8):
+    q, cache8, scales = _c(q, np.uint16), _c(cache8, np.uint8), _c(scales, np.float32)
+    pos, qstart, rids, bt = _c(pos, np.int32), _c(qstart, np.int32), _c(decode_rids, np.int32), _c(bt, np.int32)
+    out = np.zeros((rows, n_heads * 128), np.uint16)
+    orc.orc_attn_decode_fp8(_p(q, _pu16), q_stride, _p(cache8, _pu8), _p(scales, _pf), _p(out, _pu16), n_heads, n_kv,
+                            _p(pos, _pi), _p(qstart, _pi), _p(rids, _pi), len(rids), _p(bt, _pi), bt.shape[1],
+                            C.c_float(scale), nthreads)
+    return out
+
+
 def attn_prefill(q, q_stride, cache, n_heads, n_kv, pos, qstart, qlen, rids, bt, scale, rows, mirror_p=0,
                  nthreads=8, q_elem_off=0):
     q, cache = _c(q, np.uint16), _c(cache, np.uint16)
