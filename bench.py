@@ -578,6 +578,68 @@ def run_cfg4(a, dev, peak, peak_src):
                          "launch_us": round(ms * 1e3 / b.layers, 2)}}
 
 
+def run_fp8(a, dev, peak, peak_src):
+    """Configuration 2 over an fp8 (e4m3) KV cache on one GPU: the same batch and contexts, half the KV
+    bytes plus one fp32 scale per (token, kv head, plane); attention only, launches that wait for nothing,
+    over 8 layers with their own pools (4.3 GiB, larger than L2). Reports the byte rate against the HBM
+    roofline and tokens/s/layer beside the bf16 kernel's."""
+    import flashqwen_b200 as fq
+
+    layers = 8
+    rng = np.random.default_rng(a.seed)
+    lengths = rng.integers(1, a.max_ctx + 1, size=a.batch).tolist()
+    max_blocks = (a.max_ctx + PAGE - 1) // PAGE
+    num_blocks = a.batch * max_blocks
+    perm = rng.permutation(num_blocks).astype(np.int32)
+    bt = np.zeros((a.batch, max_blocks), np.int32)
+    used = 0
+    for s_, L in enumerate(lengths):
+        nb = (L + PAGE - 1) // PAGE
+        bt[s_, :nb] = perm[used:used + nb]
+        used += nb
+    g = torch.Generator(device=dev).manual_seed(a.seed + 5)
+    pools, scales = [], []
+    for _ in range(layers):
+        # e4m3 bytes without the two NaN patterns: magnitude 0..0x7E and a random sign
+        t = torch.randint(0, 0x7F, (num_blocks, 2, PAGE, KV_DIM), generator=g, device=dev, dtype=torch.uint8)
+        t |= torch.randint(0, 2, t.shape, generator=g, device=dev, dtype=torch.uint8) << 7
+        pools.append(t)
+        scales.append(torch.empty((num_blocks, N_KV, 2, PAGE), device=dev).uniform_(0.002, 0.01, generator=g))
+    q = torch.randn((layers, a.batch, Q_DIM), generator=g, device=dev).to(torch.bfloat16)
+    out = torch.zeros((layers, a.batch, Q_DIM), dtype=torch.bfloat16, device=dev)
+    d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)  # noqa: E731
+    bt_d, pos_d = d(bt), d(np.asarray([L - 1 for L in lengths], np.int32))
+    ar = d(np.arange(a.batch, dtype=np.int32))
+    slots = fq.decode_partial_slots(a.batch, N_HEADS, max_blocks)
+    pm, pl, pa = torch.empty(slots, device=dev), torch.empty(slots, device=dev), torch.empty(slots * HD, device=dev)
+    fq.device_status_reset()
+
+    def step():
+        for layer in range(layers):
+            fq.attn_decode_fp8(q[layer], Q_DIM, pools[layer], scales[layer], num_blocks, out[layer], N_HEADS, N_KV, HD,
+                               pos_d, ar, ar, a.batch, bt_d, max_blocks, PAGE, HD ** -0.5, pm, pl, pa, slots, None,
+                               INDEPENDENT)
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms = event_ms(step, max(a.steps, 10), a.warmup)
+    clocks = sampler.stop()
+    fq.device_status()
+    assert torch.isfinite(out.float()).all()
+    sum_ctx = int(sum(lengths))
+    nbytes = sum_ctx * (2 * KV_DIM + 2 * N_KV * 4) + a.batch * 2 * Q_DIM * 2   # e4m3 K+V, their scales, q in, out
+    gbs = nbytes * layers / (ms * 1e-3) / 1e9
+    layer_s = ms * 1e-3 / layers
+    return {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
+            "dtype": "e4m3 KV (f16 MMA, fp32 accumulate)", "tokens_per_s_per_layer": round(a.batch / layer_s, 1),
+            "config": {"workload": f"cfg2 over an fp8 cache: decode batch {a.batch}, ctx U[1,{a.max_ctx}], {layers} layers",
+                       "bytes_per_layer": nbytes, "sum_ctx": sum_ctx, "l2": "4.3 GiB of pools walked per step, larger than L2"},
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                         "traffic": None, "peak_source": peak_src, "launch_us": round(layer_s * 1e6, 2),
+                         "algorithmic_bytes_per_launch": nbytes}}
+
+
 def gather_check(w, a, world, rank, out_layer0, dev):
     """Outside the timed region, N > 1: rank 0 holds 4 sequences x all 32 heads of layer 0's REASSEMBLED
     output against the oracle. The K/V pages and q rows of those sequences are collected from the ranks'
@@ -961,6 +1023,7 @@ def main():
             sec = argparse.Namespace(**vars(a))
             sec.steps, sec.warmup = max(a.steps, 20), max(a.warmup, 3)
             line["secondary"] = {"cfg4_long_context_decode": run_cfg4(sec, dev, peak, peak_src),
+                                 "cfg2_fp8_kv_decode": run_fp8(sec, dev, peak, peak_src),
                                  "cfg3_append_prefill": run_cfg3(sec, dev),
                                  "cfg5_block_copies": run_copy(sec, dev)}
     print(json.dumps(line))
