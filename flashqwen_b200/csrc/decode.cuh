@@ -128,7 +128,8 @@ struct DecodeSmem {
   static constexpr int kFlatOff = kROff + MAXD * 4;
   static constexpr int kQposOff = kFlatOff + MAXD * 4;
   static constexpr int kCumOff = kQposOff + MAXD * 4;
-  static constexpr int kTotal = kCumOff + (MAXD + 1) * 4;
+  static constexpr int kArriveOff = kCumOff + (MAXD + 1) * 4;  // warps of this CTA that are through (reassembly)
+  static constexpr int kTotal = kArriveOff + 4;
   static constexpr int kAlloc = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -335,6 +336,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   int* s_flat = reinterpret_cast<int*>(smem + L::kFlatOff);
   int* s_qpos = reinterpret_cast<int*>(smem + L::kQposOff);
   int* s_cum = reinterpret_cast<int*>(smem + L::kCumOff);
+  unsigned* s_arrive = reinterpret_cast<unsigned*>(smem + L::kArriveOff);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_decode = P.n_decode;
@@ -347,6 +349,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     tma_prefetch_desc(&tmap);
     for (int i = 0; i < NW * NS; ++i) mbar_init(&bars[i], 1);
     mbar_fence_init();
+    *s_arrive = 0u;
   }
   // ---- per-sequence metadata and the page prefix sum ----
   // With a step plan (built once per step, the same for all layers) this is one coalesced load;
@@ -535,6 +538,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     if constexpr (FP8) load_q8(dst, di); else load_q(dst, di);
   };
 
+  bool wrote_rows = blockIdx.x == 0 && P.kvh_base == 0;  // CTA 0 may have written the zero rows above
   ItemCursor cc;
   item_at(cc, lo, hi, n_decode, s_cum);
   int cslot = 0;
@@ -731,6 +735,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
     if (whole) {
       // the pair lies inside this segment: straight from registers to `out`
+      wrote_rows = true;
       if (g < kGroup) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         if constexpr (!FP8) {
@@ -804,6 +809,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last) {
         merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
+        wrote_rows = true;
         if (lane == 0) *ctr = 0ull;
       }
     }
@@ -815,15 +821,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     }
   }
   // ---- reassembly: tell every rank that this rank's rows of the launch are in its buffer ----
+  // One fence per warp, and only in warps that stored rows: the warp barrier orders the lanes' stores
+  // before lane 0's fence, which is cumulative over them (the pattern of a grid-wide barrier). The fence
+  // is device-scope -- it returns when the stores have been performed, wherever their memory is; the one
+  // system-scope release is the flag store of the launch's last warp. Arrivals are counted per CTA in
+  // shared memory first and then with ONE plain atomic add per CTA on the slot's word (hundreds of warps
+  // in a compare-and-swap loop on one word serialise for tens of microseconds); the last CTA puts the word
+  // back to zero, which is why two launches that can overlap must not share a slot.
   if (P.n_peers > 0) {
-    __threadfence_system();  // this thread's stores to the peers are performed before its warp arrives
     __syncwarp();
-    if (lane == 0 && take_ticket_is_last(P.arrive, P.epoch, static_cast<int>(gridDim.x) * NW)) {
-      *P.arrive = 0ull;  // ready for a replay with the same launch number
-      const unsigned v = atomicAdd(P.seq, 1u) + 1u;
-      __threadfence_system();
-      for (int r = 0; r < P.n_peers; ++r)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flag[r]), "r"(v) : "memory");
+    if (lane == 0) {
+      if (wrote_rows) __threadfence();
+      if (atomicAdd(s_arrive, 1u) + 1u == static_cast<unsigned>(NW)) {
+        __threadfence();
+        unsigned* word = reinterpret_cast<unsigned*>(P.arrive);
+        if (atomicAdd(word, 1u) + 1u == gridDim.x) {
+          *word = 0u;
+          const unsigned v = atomicAdd(P.seq, 1u) + 1u;
+          __threadfence_system();
+          for (int r = 0; r < P.n_peers; ++r)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flag[r]), "r"(v) : "memory");
+        }
+      }
     }
   }
   // A kernel never completes before the one launched ahead of it: one warp of CTA 0 stays until that

@@ -217,7 +217,7 @@ int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const f
  * fqb_gather_control_bytes(slots, world) bytes with fqb_peer_alloc, exports them (fqb_peer_export, 64-byte
  * handles passed through any host channel) and opens the others' (fqb_peer_open). A slot is one
  * independent sequence of publishes (one per layer, say). All ranks make the same calls in the same
- * order. A rank may overwrite a peer's buffer of slot s as soon as it reaches its next call for s: put the
+ * order. Two calls of one rank whose kernels can overlap (FQB_DECODE_INDEPENDENT) must use different slots. A rank may overwrite a peer's buffer of slot s as soon as it reaches its next call for s: put the
  * consumer of a slot (and a fqb_gather_wait) on every rank's stream before that rank's next call for it.
  * The calls take no CUDA graph parameters that change between replays, so they can be captured. */
 #define FQB_PEER_HANDLE_BYTES 64

@@ -159,3 +159,45 @@ def test_norm_rope_append_prefill_match_reference_kernels():
     mirror = O.attn_prefill(ref_qkv, c.q_stride, c.cache, c.n_heads, c.n_kv, c.pos, c.qstart, c.qlen,
                             c.prefill_rids, c.bt, c.scale, rows=c.rows, mirror_p=1)
     assert maxabs(mirror, g["prefill_out"]) <= TOL
+
+
+def test_e4m3_rounding_of_the_fp8_format_is_exact_on_the_host():
+    """The fp8 KV format's byte rounding, restated in the oracle: every finite byte round-trips, a value
+    half-way between two neighbours goes to the even one, one float below / above goes down / up, and
+    everything from 464 up saturates at 448."""
+    vals = [O.orc.orc_e4m3_to_f32(b) for b in range(256)]
+    for b in range(256):
+        if (b & 0x7F) == 0x7F:
+            assert np.isnan(vals[b])
+            continue
+        assert O.orc.orc_f32_to_e4m3(vals[b]) == b
+    pos = [vals[b] for b in range(0x7F)]
+    assert pos == sorted(pos) and pos[-1] == 448.0 and pos[1] == 2.0 ** -9
+    for b in range(0x7E):
+        lo, hi = np.float32(pos[b]), np.float32(pos[b + 1])
+        mid = np.float32((lo + hi) / 2)
+        assert O.orc.orc_f32_to_e4m3(mid) == (b if b % 2 == 0 else b + 1)
+        assert O.orc.orc_f32_to_e4m3(np.nextafter(mid, np.float32(0))) == b
+        assert O.orc.orc_f32_to_e4m3(np.nextafter(mid, np.float32(1e9))) == b + 1
+    assert O.orc.orc_f32_to_e4m3(463.9) == 0x7E and O.orc.orc_f32_to_e4m3(1e30) == 0x7E
+    assert O.orc.orc_f32_to_e4m3(-1e30) == 0xFE and O.orc.orc_f32_to_e4m3(-0.0) == 0x80
+
+
+def test_fp8_append_and_decode_agree_with_the_bf16_path_up_to_the_format():
+    c = synth.decode_case([40, 300, 17], 30, seed=5, n_kv=2, poison=False)
+    rows_k = np.concatenate([c.cache[np.asarray(c.tables[s])[np.arange(L) // 16], 0, np.arange(L) % 16] for s, L in enumerate(c.lengths)])
+    rows_v = np.concatenate([c.cache[np.asarray(c.tables[s])[np.arange(L) // 16], 1, np.arange(L) % 16] for s, L in enumerate(c.lengths)])
+    rows = np.concatenate([rows_k, rows_v], 1)
+    req = np.concatenate([np.full(L, s) for s, L in enumerate(c.lengths)]).astype(np.int32)
+    pos = np.concatenate([np.arange(L) for L in c.lengths]).astype(np.int32)
+    cache8 = np.zeros(c.cache.shape, np.uint8)
+    scales = np.zeros((c.num_blocks, 2, 2, 16), np.float32)
+    O.kv_append_fp8(cache8, scales, rows, 512, 0, 256, c.bt, req, pos)
+    # a stored value reads back within half an e4m3 step of its row maximum's scale
+    back = np.vectorize(O.orc.orc_e4m3_to_f32)(cache8[c.tables[1][0], 0, 3, :128]).astype(np.float32) * scales[c.tables[1][0], 0, 0, 3]
+    want = synth.bf16_to_f32(c.cache[c.tables[1][0], 0, 3, :128])
+    assert np.max(np.abs(back - want)) <= np.max(np.abs(want)) * 2.0 ** -4
+    got = O.attn_decode_fp8(c.qkv, c.q_stride, cache8, scales, c.n_heads, c.n_kv, c.pos, c.qstart, c.decode_rids, c.bt,
+                            c.scale, rows=3)
+    ref = O.attn_decode(c.qkv, c.q_stride, c.cache, c.n_heads, c.n_kv, c.pos, c.qstart, c.decode_rids, c.bt, c.scale, rows=3)
+    assert maxabs(got, ref) <= 0.15
