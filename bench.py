@@ -87,9 +87,10 @@ def parse():
                     help="which launch mode the headline value is taken in (all three are reported under `modes`)")
     ap.add_argument("--only-mode", action="store_true", help="time the headline mode only")
     ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (cfg4, cfg3, block copies)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "cfg3", "copy"],
-                    help="decode: the headline step. cfg3: KV append + chunked prefill (4 x 512-row chunks over "
-                         "histories 0/1024/3000/7000). copy: prefix-block copy-on-write copies over 36 layers")
+    ap.add_argument("--workload", default="decode", choices=["decode", "cfg3", "copy", "cfg4", "fp8"],
+                    help="decode: the headline step. The others run one of its secondary workloads alone: cfg3 (KV append "
+                         "+ chunked prefill, 4 x 512-row chunks over histories 0/1024/3000/7000), copy (prefix-block "
+                         "copy-on-write copies over 36 layers), cfg4 (decode batch 8 x 32768), fp8 (config 2 over an e4m3 cache)")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="tuning aid: run rank 0's share of an N-way kv-head shard on this one GPU")
     a = ap.parse_args()
@@ -554,7 +555,7 @@ def run_cfg4(a, dev, peak, peak_src):
     """Configuration 4 on one GPU: batch 8 at 32768 tokens each (1 GiB of KV per layer), attention only,
     launches that wait for nothing, over 6 layers with their own pools (6 GiB, larger than L2)."""
     b = argparse.Namespace(**vars(a))
-    b.batch, b.fixed_ctx, b.layers, b.shard_of = 8, 32768, 6, 0
+    b.batch, b.fixed_ctx, b.layers, b.shard_of = 8, 32768, min(a.layers, 6), 0
     w = Workload(b, 0, 1, dev)
     r = FqbRunner(w)
 
@@ -585,7 +586,7 @@ def run_fp8(a, dev, peak, peak_src):
     roofline and tokens/s/layer beside the bf16 kernel's."""
     import flashqwen_b200 as fq
 
-    layers = 8
+    layers = min(a.layers, 8)
     rng = np.random.default_rng(a.seed)
     lengths = rng.integers(1, a.max_ctx + 1, size=a.batch).tolist()
     max_blocks = (a.max_ctx + PAGE - 1) // PAGE
@@ -633,7 +634,8 @@ def run_fp8(a, dev, peak, peak_src):
     return {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
             "dtype": "e4m3 KV (f16 MMA, fp32 accumulate)", "tokens_per_s_per_layer": round(a.batch / layer_s, 1),
             "config": {"workload": f"cfg2 over an fp8 cache: decode batch {a.batch}, ctx U[1,{a.max_ctx}], {layers} layers",
-                       "bytes_per_layer": nbytes, "sum_ctx": sum_ctx, "l2": "4.3 GiB of pools walked per step, larger than L2"},
+                       "bytes_per_layer": nbytes, "sum_ctx": sum_ctx,
+                       "l2": f"{layers} pools of 0.54 GB walked per step, larger than L2"},
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                          "traffic": None, "peak_source": peak_src, "launch_us": round(layer_s * 1e6, 2),
@@ -685,7 +687,11 @@ def main():
         if int(os.environ.get("RANK", "0")) != 0:
             return
         torch.cuda.set_device(0)
-        print(json.dumps((run_cfg3 if a.workload == "cfg3" else run_copy)(a, torch.device("cuda", 0))))
+        dev0 = torch.device("cuda", 0)
+        peak0, src0 = hbm_peak()
+        one = {"cfg3": lambda: run_cfg3(a, dev0), "copy": lambda: run_copy(a, dev0),
+               "cfg4": lambda: run_cfg4(a, dev0, peak0, src0), "fp8": lambda: run_fp8(a, dev0, peak0, src0)}[a.workload]
+        print(json.dumps(one()))
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

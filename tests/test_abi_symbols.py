@@ -90,3 +90,22 @@ def test_engine_launchers_refuse_to_run_before_configure():
     assert _lib.lib.fqb_engine_status() == 0
     _lib.engine_symbol("LaunchAttnDecodeCute")(1, 6144, 1, 1, 32, 8, 64, 1, 1, 1, 4, 1, 8, 16, 0.1, 1, 1, 1, None)
     assert _lib.lib.fqb_engine_status() == -2 and b"head_dim" in _lib.lib.fqb_engine_error()
+
+
+def test_reassembly_control_block_layout_and_argument_checks_without_gpu():
+    """fqb_gather_control_bytes: flags [slots][world] + publish counters [slots] (32-bit), then 8-byte aligned
+    arrival words [slots]; bad descriptors are refused before any CUDA call."""
+    from flashqwen_b200 import _lib, peer
+
+    for slots, world in ((1, 1), (36, 8), (3, 2), (5, 4)):
+        words = slots * world + slots
+        words += words & 1
+        assert _lib.lib.fqb_gather_control_bytes(slots, world) == words * 4 + slots * 8
+    assert _lib.lib.fqb_gather_control_bytes(4, 9) == 0 and _lib.lib.fqb_gather_control_bytes(0, 2) == 0
+    g = peer.Gather()
+    g.world, g.rank, g.slots, g.slot = 2, 0, 4, 7        # slot outside the block
+    g.control = 4096
+    assert _lib.lib.fqb_gather_wait(ctypes.addressof(g), None) == -1
+    g.slot, g.control = 0, None
+    assert _lib.lib.fqb_gather_wait_all(ctypes.addressof(g), None) == -1
+    assert _lib.lib.fqb_peer_export(None, None) == -1 and _lib.lib.fqb_peer_open(None, None) == -1
