@@ -145,6 +145,12 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
   asm("{\n\t.reg .b16 s;\n\tcvt.u16.u32 s, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, s;\n\t}" : "=r"(r) : "r"(two_bytes));
   return r;
 }
+// four e4m3 bytes -> two f16x2 words (bytes 0,1 and bytes 2,3); exact
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t four_bytes, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(four_bytes));
+}
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -617,17 +617,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
         float mx = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float mnew = fmaxf(m, mx);
-        const float corr = fast_exp2(m - mnew);
-        m = mnew;
-        const float p00 = fast_exp2(x00 - mnew), p01 = fast_exp2(x01 - mnew);
-        const float p10 = fast_exp2(x10 - mnew), p11 = fast_exp2(x11 - mnew);
-        l = l * corr + ((p00 + p01) + (p10 + p11));
+        // the running maximum moves on the first pages of a sequence and rarely afterwards: the
+        // accumulator is rescaled only on pages where some row's maximum grew
+        if (__any_sync(0xffffffffu, mx > m)) {
+          const float mnew = fmaxf(m, mx);
+          const float corr = fast_exp2(m - mnew);
+          m = mnew;
+          l *= corr;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          o[j][0] *= corr;
-          o[j][1] *= corr;
+          for (int j = 0; j < 16; ++j) {
+            o[j][0] *= corr;
+            o[j][1] *= corr;
+          }
         }
+        const float p00 = fast_exp2(x00 - m), p01 = fast_exp2(x01 - m);
+        const float p10 = fast_exp2(x10 - m), p11 = fast_exp2(x11 - m);
+        l += (p00 + p01) + (p10 + p11);
         const uint32_t pa0 = pack_bf16(p00, p01), pa2 = pack_bf16(p10, p11);
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
@@ -664,8 +669,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           }
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            mma_f16(s0, qa[ks][0], 0u, qa[ks][1], 0u, e4m3x2_to_f16x2(kw[0][ks]), e4m3x2_to_f16x2(kw[0][ks] >> 16));
-            mma_f16(s1, qa[ks][0], 0u, qa[ks][1], 0u, e4m3x2_to_f16x2(kw[1][ks]), e4m3x2_to_f16x2(kw[1][ks] >> 16));
+            uint32_t b0, b1, b2, b3;
+            e4m3x4_to_f16x2x2(kw[0][ks], b0, b1);
+            e4m3x4_to_f16x2x2(kw[1][ks], b2, b3);
+            mma_f16(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            mma_f16(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
           }
         }
         const float2 ka = *reinterpret_cast<const float2*>(sc + 2 * t), kb = *reinterpret_cast<const float2*>(sc + 8 + 2 * t);
@@ -681,17 +689,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
         float mx = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float mnew = fmaxf(m, mx);
-        const float corr = fast_exp2(m - mnew);
-        m = mnew;
-        const float p00 = fast_exp2(x00 - mnew), p01 = fast_exp2(x01 - mnew);
-        const float p10 = fast_exp2(x10 - mnew), p11 = fast_exp2(x11 - mnew);
-        l = l * corr + ((p00 + p01) + (p10 + p11));
+        if (__any_sync(0xffffffffu, mx > m)) {  // rescale only where some row's maximum grew
+          const float mnew = fmaxf(m, mx);
+          const float corr = fast_exp2(m - mnew);
+          m = mnew;
+          l *= corr;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          o[j][0] *= corr;
-          o[j][1] *= corr;
+          for (int j = 0; j < 16; ++j) {
+            o[j][0] *= corr;
+            o[j][1] *= corr;
+          }
         }
+        const float p00 = fast_exp2(x00 - m), p01 = fast_exp2(x01 - m);
+        const float p10 = fast_exp2(x10 - m), p11 = fast_exp2(x11 - m);
+        l += (p00 + p01) + (p10 + p11);
         const uint32_t pa0 = pack_f16(p00 * (va.x * kPScale8), p01 * (va.y * kPScale8));
         const uint32_t pa2 = pack_f16(p10 * (vb.x * kPScale8), p11 * (vb.y * kPScale8));
         // ---- O += P V: value tokens 2t, 2t+1, 2t+8, 2t+9, dims 16g .. 16g+15 (accumulator tile j = dim 16g+j) ----
@@ -708,10 +719,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           // bytes (j, j+1) of rows 0/1 interleaved, then (j+2, j+3): two key pairs per permute
           const uint32_t e01a = __byte_perm(vr[0][wd], vr[1][wd], 0x5140), e01b = __byte_perm(vr[0][wd], vr[1][wd], 0x7362);
           const uint32_t e23a = __byte_perm(vr[2][wd], vr[3][wd], 0x5140), e23b = __byte_perm(vr[2][wd], vr[3][wd], 0x7362);
-          mma_f16(o[4 * wd + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01a), e4m3x2_to_f16x2(e23a));
-          mma_f16(o[4 * wd + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01a >> 16), e4m3x2_to_f16x2(e23a >> 16));
-          mma_f16(o[4 * wd + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01b), e4m3x2_to_f16x2(e23b));
-          mma_f16(o[4 * wd + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(e01b >> 16), e4m3x2_to_f16x2(e23b >> 16));
+          uint32_t u0, u1, u2, u3, w0, w1, w2, w3;
+          e4m3x4_to_f16x2x2(e01a, u0, u1);
+          e4m3x4_to_f16x2x2(e23a, w0, w1);
+          e4m3x4_to_f16x2x2(e01b, u2, u3);
+          e4m3x4_to_f16x2x2(e23b, w2, w3);
+          mma_f16(o[4 * wd + 0], pa0, 0u, pa2, 0u, u0, w0);
+          mma_f16(o[4 * wd + 1], pa0, 0u, pa2, 0u, u1, w1);
+          mma_f16(o[4 * wd + 2], pa0, 0u, pa2, 0u, u2, w2);
+          mma_f16(o[4 * wd + 3], pa0, 0u, pa2, 0u, u3, w3);
         }
       }
       __syncwarp();  // every lane has read the buffer before it is refilled
