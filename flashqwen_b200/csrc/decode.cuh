@@ -813,8 +813,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           P.pm[slot0 + g] = m;
           P.pl[slot0 + g] = l;
         }
-        __threadfence();
       }
+      // one fence for the warp: the warp barrier orders the lanes' stores before lane 0's fence, which is
+      // cumulative over them (every lane fencing for itself cost about a microsecond per cut sequence)
       __syncwarp();
       int last = 0;
       if (lane == 0) {
