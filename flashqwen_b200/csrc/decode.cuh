@@ -36,6 +36,7 @@
 namespace fqb {
 
 constexpr int kMaxPeers = 8;
+constexpr int kMaxPending = 8;  // cut sequences a warp may leave behind before it settles them (<= 32)
 
 struct DecodeParams {
   const __nv_bfloat16* q;
@@ -129,7 +130,8 @@ struct DecodeSmem {
   static constexpr int kQposOff = kFlatOff + MAXD * 4;
   static constexpr int kCumOff = kQposOff + MAXD * 4;
   static constexpr int kArriveOff = kCumOff + (MAXD + 1) * 4;  // warps of this CTA that are through (reassembly)
-  static constexpr int kTotal = kArriveOff + 4;
+  static constexpr int kPendOff = kArriveOff + 4;              // per warp: cut sequences whose ticket is still to be taken
+  static constexpr int kTotal = kPendOff + NW * kMaxPending * 4;
   static constexpr int kAlloc = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -337,6 +339,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   int* s_qpos = reinterpret_cast<int*>(smem + L::kQposOff);
   int* s_cum = reinterpret_cast<int*>(smem + L::kCumOff);
   unsigned* s_arrive = reinterpret_cast<unsigned*>(smem + L::kArriveOff);
+  int* s_pend = reinterpret_cast<int*>(smem + L::kPendOff) + (threadIdx.x >> 5) * kMaxPending;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_decode = P.n_decode;
@@ -539,6 +542,38 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   };
 
   bool wrote_rows = blockIdx.x == 0 && P.kvh_base == 0;  // CTA 0 may have written the zero rows above
+  // A sequence cut by segment boundaries costs its warp a fence, an atomic round trip and, for the last
+  // arriver, a merge: about 6 us measured, during which the warp's ring stands still. So the partial
+  // is only stored when the item ends; the tickets are taken later -- when the warp has no more pages to
+  // stream (or kMaxPending items are waiting) -- for all waiting items at once, one lane per item, their
+  // round trips in flight together; then the merges this warp has won, one after the other.
+  int n_pend = 0;
+  auto settle = [&]() {
+    __syncwarp();  // the lanes' partial stores are ordered before the fences below
+    int di_mine = -1, b0 = 0, b1 = 0, last = 0;
+    if (lane < n_pend) {
+      di_mine = s_pend[lane];
+      const int first = s_cum[di_mine], np_seq = s_cum[di_mine + 1] - first;
+      b0 = first / W;
+      b1 = (first + np_seq - 1) / W;
+      unsigned long long* c = counters + static_cast<long long>(di_mine) * P.n_kv + kvh;
+      __threadfence();
+      last = take_ticket_is_last(c, P.epoch, b1 - b0 + 1) ? 1 : 0;
+      __threadfence();
+    }
+    unsigned won = __ballot_sync(0xffffffffu, last != 0);
+    while (won) {
+      const int src = __ffs(won) - 1;
+      won &= won - 1;
+      const int di = __shfl_sync(0xffffffffu, di_mine, src);
+      const int sb0 = __shfl_sync(0xffffffffu, b0, src), sb1 = __shfl_sync(0xffffffffu, b1, src);
+      merge_pair(P, di, kvh, sb0, sb1, s_flat[di], lane);
+      wrote_rows = true;
+      if (lane == 0) counters[static_cast<long long>(di) * P.n_kv + kvh] = 0ull;
+    }
+    n_pend = 0;
+    __syncwarp();
+  };
   ItemCursor cc;
   item_at(cc, lo, hi, n_decode, s_cum);
   int cslot = 0;
@@ -747,8 +782,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
         o[j][1] *= 1.f / kPScale8;
       }
     }
-    const int b0 = whole ? 0 : s_cum[cc.di] / W, b1 = whole ? 0 : (s_cum[cc.di] + cc.np - 1) / W;  // segments that see this sequence
-    unsigned long long* ctr = counters + static_cast<long long>(cc.di) * P.n_kv + kvh;
     if (whole) {
       // the pair lies inside this segment: straight from registers to `out`
       wrote_rows = true;
@@ -814,22 +847,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           P.pl[slot0 + g] = l;
         }
       }
-      // one fence for the warp: the warp barrier orders the lanes' stores before lane 0's fence, which is
-      // cumulative over them (every lane fencing for itself cost about a microsecond per cut sequence)
-      __syncwarp();
-      int last = 0;
-      if (lane == 0) {
-        __threadfence();
-        last = take_ticket_is_last(ctr, P.epoch, b1 - b0 + 1) ? 1 : 0;
-        __threadfence();
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        merge_pair(P, cc.di, kvh, b0, b1, flat, lane);
-        wrote_rows = true;
-        if (lane == 0) *ctr = 0ull;
-      }
+      if (lane == 0) s_pend[n_pend] = cc.di;
+      ++n_pend;
     }
+    if (n_pend == kMaxPending || (nx.off >= hi && n_pend > 0)) settle();
     cc = nx;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
