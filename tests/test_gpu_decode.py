@@ -393,3 +393,37 @@ def test_fused_step_in_a_cuda_graph_replays_after_the_sequences_grew():
                 c.bt[sq, c.pos[sq] // 16] = free.pop()
         c.qkv = synth.f32_to_bf16(rng.standard_normal(c.qkv.shape, dtype=np.float32))
         pos.copy_(dv(c.pos)); bt.copy_(dv(c.bt)); qkv.copy_(dv(c.qkv))
+
+
+@pytest.mark.parametrize("flags", [0, 2])
+@pytest.mark.parametrize("n_kv,lengths", [(8, [7000, 9000, 17, 5000, 2100, 33, 4100]),
+                                          (2, [30000, 9000, 17, 25000, 2100, 33, 14100, 1]),
+                                          (1, [60000, 50001, 17, 45000, 3])])
+def test_long_page_lists_fused_and_replayed(flags, n_kv, lengths):
+    """Page lists several times longer than the launch has warp groups: every sequence is cut over many
+    segments, some segments hold the ends of several sequences. Calls with changing launch tags and
+    replays of a captured call (same tag: the arrival counters must have been put back) all give the
+    oracle's rows, and the fused append writes the cache bit-exactly."""
+    blocks = sum((L + 15) // 16 for L in lengths) + 8
+    c, before, after = _fused_case(lengths, blocks, seed=700 + n_kv, n_kv=n_kv)
+    cache, qkv = dv(before), dv(c.qkv)
+    meta = (dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt))
+    out = torch.full((len(lengths), c.n_heads * 128), 0x7FC0, dtype=torch.int16, device=DEV)
+    s = Scratch(len(lengths), c.n_heads, c.max_blocks)
+    for _ in range(2):
+        _fused_call(c, cache, qkv, out, s, flags=flags, meta=meta)
+    torch.cuda.synchronize()
+    fq.device_status()
+    assert np.array_equal(host(cache), after)
+    c.cache = after
+    want = oracle_decode(c)
+    assert maxabs(host(out), want) <= TOL
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        _fused_call(c, cache, qkv, out, s, flags=flags, meta=meta)
+    for _ in range(3):
+        out.fill_(0x7FC0)
+        g.replay()
+        torch.cuda.synchronize()
+        fq.device_status()
+        assert maxabs(host(out), want) <= TOL
