@@ -21,7 +21,8 @@
 //     V MN-major) with P read from tensor memory: the softmax overwrites the first 32 columns of its
 //     S tile with packed bf16 pairs.
 //   * Softmax warps: thread = one row (one TMEM lane): tcgen05.ld of its 64 scores, causal mask,
-//     running max without any shuffle, exp2, P -> bf16. The accumulator is rescaled in TMEM only
+//     running max without any shuffle (three-input max), scale and subtract, sums as two-wide fp32
+//     instructions, exp2, P -> bf16. The accumulator is rescaled in TMEM only
 //     when a row's max grew by more than 2^8 since the scale in use (the probabilities stay exact
 //     relative to that scale).
 // Completion is tracked with mbarriers (tcgen05.commit for MMA groups); every wait is bounded and
@@ -226,11 +227,11 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < kTcBN; j += 4) {
-        mx0 = fmaxf(mx0, x[j]);
-        mx1 = fmaxf(mx1, x[j + 1]);
-        mx2 = fmaxf(mx2, x[j + 2]);
-        mx3 = fmaxf(mx3, x[j + 3]);
+      for (int j = 0; j < kTcBN; j += 8) {
+        mx0 = fmax3(mx0, x[j], x[j + 1]);
+        mx1 = fmax3(mx1, x[j + 2], x[j + 3]);
+        mx2 = fmax3(mx2, x[j + 4], x[j + 5]);
+        mx3 = fmax3(mx3, x[j + 6], x[j + 7]);
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2;
       const float m_new = fmaxf(m_used, mx);
@@ -240,20 +241,21 @@ prefill_tc_ks_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPara
         m_used = m_new;
         l *= f;
       }
-      float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
+      float2 sm0 = make_float2(0.f, 0.f), sm1 = make_float2(0.f, 0.f);
       float pf[kTcBN / 2];
-      const float neg_m = -m_used;
+      const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(-m_used, -m_used);
 #pragma unroll
       for (int j = 0; j < kTcBN; j += 4) {
-        const float p0 = fast_exp2(fmaf(x[j], P.scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(x[j + 1], P.scale_log2, neg_m));
-        const float p2 = fast_exp2(fmaf(x[j + 2], P.scale_log2, neg_m));
-        const float p3 = fast_exp2(fmaf(x[j + 3], P.scale_log2, neg_m));
-        sm0 += p0; sm1 += p1; sm2 += p2; sm3 += p3;
-        pf[j >> 1] = __uint_as_float(pack_bf16(p0, p1));
-        pf[(j >> 1) + 1] = __uint_as_float(pack_bf16(p2, p3));
+        float2 e0 = ffma2(make_float2(x[j], x[j + 1]), sc2, nm2);
+        float2 e1 = ffma2(make_float2(x[j + 2], x[j + 3]), sc2, nm2);
+        e0.x = fast_exp2(e0.x); e0.y = fast_exp2(e0.y);
+        e1.x = fast_exp2(e1.x); e1.y = fast_exp2(e1.y);
+        sm0 = fadd2(sm0, e0);
+        sm1 = fadd2(sm1, e1);
+        pf[j >> 1] = __uint_as_float(pack_bf16(e0.x, e0.y));
+        pf[(j >> 1) + 1] = __uint_as_float(pack_bf16(e1.x, e1.y));
       }
-      l += (sm0 + sm1) + (sm2 + sm3);
+      l += (sm0.x + sm0.y) + (sm1.x + sm1.y);
       const bool any_grow = i > 0 && __any_sync(0xffffffffu, grow);
       if (any_grow) {  // PV of the tile before must have finished before O is rescaled
         wait(o_done(gi, (i - 1) & 1), ((i - 1) >> 1) & 1, 1000 + k);

@@ -52,7 +52,9 @@ def test_small_case_matches_oracle_and_reference_fixture():
 
 
 @pytest.mark.parametrize("hist,chunk", [(0, 1), (0, 2), (0, 15), (0, 16), (0, 17), (0, 31), (0, 32), (0, 33), (0, 64),
-                                        (0, 65), (5, 3), (16, 16), (17, 40), (100, 7), (1000, 100), (31, 97)])
+                                        (0, 65), (5, 3), (16, 16), (17, 40), (100, 7), (1000, 100), (31, 97),
+                                        (0, 127), (0, 128), (0, 129), (100, 28), (100, 29), (250, 6), (255, 2),
+                                        (256, 33), (383, 2), (2040, 20), (127, 130)])
 def test_single_request_shapes(hist, chunk):
     if chunk == 1:
         pytest.skip("a 1-row request is a decode request by definition (qlen == 1)")
@@ -84,11 +86,11 @@ SCALES = [128 ** -0.5, float(np.nextafter(np.float32(128 ** -0.5), np.float32(0)
 
 
 @pytest.mark.parametrize("scale", SCALES)
-def test_any_softmax_scale_with_rows_that_see_nothing_of_the_upper_key_half(scale):
-    """The CTA's second warp group takes the upper half of the key tiles. Rows at the start of a query
+def test_any_softmax_scale_with_rows_that_see_nothing_of_a_key_tile(scale):
+    """The CTA's second warp group takes the upper half of the 64-key tiles. Rows at the start of a query
     tile whose positions lie below that half see none of its keys (history 60 + chunk 20: positions
-    60..63 against keys 64..127). Such a tile must leave the row untouched for every scale, not only
-    for 1/sqrt(128)."""
+    60..63 against keys 64..127; history 120 + chunk 20: positions 120..127 against keys 128..191). Such
+    a tile must leave the row untouched for every scale, not only for 1/sqrt(128)."""
     for hist, chunk, seed in ((60, 20, 1), (0, 70, 2), (130, 10, 3), (120, 20, 4), (50, 32, 5), (185, 30, 6),
                               (1000, 40, 7)):
         c = synth.prefill_case([hist], [chunk], num_blocks=(hist + chunk) // 16 + 3, seed=900 + seed, n_kv=2)
