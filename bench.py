@@ -413,6 +413,28 @@ def event_ms(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
+def event_ms_with_clocks(index, fn, steps, warmup, before=None, min_samples=3, patience_s=1.5):
+    """event_ms for regions of a few milliseconds: nvidia-smi prints its first row only some hundred
+    milliseconds after it starts, so the same work (`fn`) keeps running, untimed, until the first sample has
+    come before the timed region and until min_samples have come after it. All samples are then taken under
+    this load, around the timed region. `before` (optional) is timed first with the same sampler running and
+    its result returned in front."""
+    sampler = ClockSampler(index)
+    sampler.start()
+    t0 = time.time()
+    while len(sampler.rows) < 1 and time.time() - t0 < patience_s:
+        fn()
+        torch.cuda.synchronize()
+    first = event_ms(before, steps, warmup) if before is not None else None
+    ms = event_ms(fn, steps, warmup)
+    t0 = time.time()
+    while len(sampler.rows) < min_samples and time.time() - t0 < patience_s:
+        fn()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    return (first, ms, clocks) if before is not None else (ms, clocks)
+
+
 def tensor_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -496,11 +518,7 @@ def run_cfg3(a, dev):
     for i in range(nset):  # rows normalised + appended once so that the attention sees sane values
         it["i"] = i - 1
         append_step()
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms_app = event_ms(append_step, a.steps, a.warmup)
-    ms_pre = event_ms(prefill_step, a.steps, a.warmup)
-    clocks = sampler.stop()
+    ms_app, ms_pre, clocks = event_ms_with_clocks(dev.index or 0, prefill_step, a.steps, a.warmup, before=append_step)
     if not reference:
         fq.device_status()
     flops = float(sum(N_HEADS * 4 * HD * (p + 1) for p in pos.tolist()))
@@ -533,10 +551,7 @@ def run_copy(a, dev):
     ids = rng.permutation(num_blocks)[:2 * pairs_n].astype(np.int32)
     pairs = torch.from_numpy(np.stack([ids[:pairs_n], ids[pairs_n:]], 1).reshape(-1).copy()).to(dev)
     fn = lambda: fq.copy_blocks_layers(ptrs, layers, num_blocks, N_KV, pairs, pairs_n)  # noqa: E731
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms = event_ms(fn, a.steps, a.warmup)
-    clocks = sampler.stop()
+    ms, clocks = event_ms_with_clocks(dev.index or 0, fn, a.steps, a.warmup)
     fq.device_status()
     nbytes = 2 * pairs_n * 65536 * layers
     peak, src = hbm_peak()
@@ -564,10 +579,7 @@ def run_cfg4(a, dev, peak, peak_src):
         for layer in range(b.layers):
             r.decode(layer, w.qkv, w.bt, w.pos, w.qstart, w.rids, flags=INDEPENDENT)
 
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms = event_ms(step, max(a.steps, 10), a.warmup)
-    clocks = sampler.stop()
+    ms, clocks = event_ms_with_clocks(dev.index or 0, step, max(a.steps, 10), a.warmup)
     r.check()
     gbs = w.bytes_layer_total * b.layers / (ms * 1e-3) / 1e9
     return {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
@@ -621,10 +633,7 @@ def run_fp8(a, dev, peak, peak_src):
                                pos_d, ar, ar, a.batch, bt_d, max_blocks, PAGE, HD ** -0.5, pm, pl, pa, slots, None,
                                INDEPENDENT)
 
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms = event_ms(step, max(a.steps, 10), a.warmup)
-    clocks = sampler.stop()
+    ms, clocks = event_ms_with_clocks(dev.index or 0, step, max(a.steps, 10), a.warmup)
     fq.device_status()
     assert torch.isfinite(out.float()).all()
     sum_ctx = int(sum(lengths))

@@ -193,6 +193,14 @@ using Decode8Cfg8 = DecodeCfg<8, 6, 8, 1, 512>;
 using Decode8Cfg4 = DecodeCfg<4, 6, 4, 2, 256>;
 using Decode8Cfg2 = DecodeCfg<4, 6, 2, 2, 256>;
 using Decode8Cfg1 = DecodeCfg<4, 6, 1, 2, 256>;
+// fp8 launches that wait for nothing: three CTAs resident per SM instead of two (rings of 4). The fp8
+// kernel is bound by the issue rate of its one warp per scheduler (unpacking e4m3 costs instructions, not
+// bytes), and 168 registers per thread hold all but 32 bytes of its state, so twelve resident warps
+// instead of eight give 5.26 instead of 4.59 TB/s on configuration 2 (0.80 instead of 0.70 of the copy
+// peak). The bf16 4-head shape gains nothing from the same change (it is at the copy peak with two).
+using Decode8Cfg4I = DecodeCfg<4, 4, 4, 3, 256>;
+using Decode8Cfg2I = DecodeCfg<4, 4, 2, 3, 256>;
+using Decode8Cfg1I = DecodeCfg<4, 4, 1, 3, 256>;
 
 // CTAs per SM of a default-mode launch of the 4-, 2- and 1-head shapes (build-time choice; measured on
 // B200 with every launch waiting for the one before it: 1 beats 2 for the 4-head and the 1-head shape).
@@ -585,9 +593,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
         const int left = n_kv - base;
         P.kvh_base = base;
         int rc, took;
-        if (left >= 4) { rc = fp8 ? launch_decode<Decode8Cfg4, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) { rc = fp8 ? launch_decode<Decode8Cfg2, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
-        else { rc = fp8 ? launch_decode<Decode8Cfg1, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg1I>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        if (left >= 4) { rc = fp8 ? launch_decode<Decode8Cfg4I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
+        else if (left >= 2) { rc = fp8 ? launch_decode<Decode8Cfg2I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
+        else { rc = fp8 ? launch_decode<Decode8Cfg1I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<DecodeCfg1I>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
         P.sync_first = 0;  // later launches of the call serve other heads: disjoint partials and counters
