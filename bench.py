@@ -227,7 +227,7 @@ class Workload:
 
 
 
-INDEPENDENT, HISTORY_STABLE = 1, 2   # FQB_DECODE_INDEPENDENT, FQB_DECODE_HISTORY_STABLE
+INDEPENDENT, HISTORY_STABLE, PUBLISH_LATER = 1, 2, 4   # FQB_DECODE_INDEPENDENT, FQB_DECODE_HISTORY_STABLE, FQB_GATHER_PUBLISH_LATER
 
 
 class FqbRunner:
@@ -926,7 +926,8 @@ def main():
                 for layer in range(l0, l1):
                     # a chunk's first launch follows a copy that wrote its rows: an event wait orders it in full
                     if peers is not None:
-                        r.fused_gather(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids, descs[layer], flags)
+                        r.fused_gather(layer, d_qkv, d_bt, d_pos, d_qstart, d_rids, descs[layer],
+                                       flags | (PUBLISH_LATER if flags == HISTORY_STABLE else 0))
                     else:
                         r.fused(layer, d_qkv, d_bt, d_req, d_pos, d_qstart, d_rids, flags=flags)
                 ev_out[i].record(main)
@@ -934,6 +935,12 @@ def main():
                     copy_out.wait_event(ev_out[i])
                     w.h_out[l0:l1].copy_(w.out[l0:l1], non_blocking=True)
             if peers is not None:
+                # Launches that wait for one another store their rows into the peers' buffers without
+                # announcing them (an announcement ends a launch with a system-wide fence and a round of
+                # flag stores over NVLink, which the next launch would wait for); one kernel announces all
+                # layers after the last one. Launches that wait for nothing announce per layer themselves.
+                if flags == HISTORY_STABLE:
+                    r.fq.gather_publish_all(descs[0])
                 r.fq.gather_wait_all(descs[0])   # every rank's rows of every layer are in this rank's buffer
             main.wait_stream(copy_out)
 
@@ -977,8 +984,8 @@ def main():
                            "and of the step metadata (one pinned buffer, one copy), per layer "
                            + ("the reference's KV append + decode attention" if reference else
                               "the fused KV append + decode attention (FQB_DECODE_HISTORY_STABLE)")
-                           + ((", every finished row stored into all ranks' buffers of full rows by the kernel, one wait "
-                               "for all layers at the end") if dist_on and peers is not None else
+                           + ((", every finished row stored into all ranks' buffers of full rows by the kernel, one "
+                               "publish and one wait for all layers at the end") if dist_on and peers is not None else
                               (", one NCCL all-gather of all layers' head outputs" if dist_on else ""))
                            + ", D2H of the output"
                            + ("; one CUDA graph per step, host sync every step" if a.graph else "")}

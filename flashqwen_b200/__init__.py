@@ -13,6 +13,7 @@ from .host import BlockAllocator, acquire_prefix, cache_blocks, cow_prepare, has
 from .ops import (  # noqa: F401
     DECODE_HISTORY_STABLE,
     DECODE_INDEPENDENT,
+    GATHER_PUBLISH_LATER,
     KvStore,
     append_attn_decode,
     append_attn_decode_gather,
@@ -28,6 +29,7 @@ from .ops import (  # noqa: F401
     device_status,
     device_status_reset,
     gather_blocks,
+    gather_publish_all,
     gather_wait,
     gather_wait_all,
     kv_append,

@@ -62,6 +62,7 @@ SIGNATURES = {
     "fqb_gather_control_bytes": (_i64, [_i, _i]),
     "fqb_gather_wait": (_i, [_p, _p]),
     "fqb_gather_wait_all": (_i, [_p, _p]),
+    "fqb_gather_publish_all": (_i, [_p, _p]),
     "fqb_peer_alloc": (_i, [_i64, _p]),
     "fqb_peer_free": (_i, [_p]),
     "fqb_peer_export": (_i, [_p, _p]),

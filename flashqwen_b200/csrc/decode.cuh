@@ -314,6 +314,33 @@ gather_wait_all_kernel(const unsigned* __restrict__ flags, const unsigned* __res
   }
 }
 
+// Publishes every slot of the control block at once: launched without overlap after the last kernel that
+// stored rows into the peers' buffers, so those stores have been performed. One thread per slot bumps the
+// slot's counter; one thread per (slot, rank) stores it into that rank's flag word for this rank.
+struct PublishAllParams {
+  unsigned* seq;               // this rank's publish counters [slots]
+  unsigned* flags[kMaxPeers];  // every rank's flag words [slots][world]
+  int slots, world, rank;
+};
+__global__ void __launch_bounds__(256)
+gather_publish_all_kernel(const PublishAllParams P) {
+  __shared__ unsigned s_seq[256];
+  const int tid = threadIdx.x;
+  for (int base = 0; base < P.slots; base += 256) {
+    const int n = min(256, P.slots - base);
+    if (tid < n) s_seq[tid] = atomicAdd(P.seq + base + tid, 1u) + 1u;
+    __threadfence_system();
+    __syncthreads();
+    for (int i = tid; i < n * P.world; i += 256) {
+      const int s = i / P.world, r = i - s * P.world;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.flags[r] + static_cast<size_t>(base + s) * P.world + P.rank),
+                   "r"(s_seq[s])
+                   : "memory");
+    }
+    __syncthreads();
+  }
+}
+
 // HEADS = local kv heads served by the launch (1, 2, 4 or 8); the CTA's NW warps form SUB = NW / HEADS
 // groups of HEADS warps, and group `sub` of CTA b owns segment b * SUB + sub of the flat page list.
 // FP8: the cache holds e4m3 bytes with one fp32 scale per (token, head, plane). A page slice is 4 KiB
@@ -866,7 +893,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   // shared memory first and then with ONE plain atomic add per CTA on the slot's word (hundreds of warps
   // in a compare-and-swap loop on one word serialise for tens of microseconds); the last CTA puts the word
   // back to zero, which is why two launches that can overlap must not share a slot.
-  if (P.n_peers > 0) {
+  if (P.n_peers > 0 && P.arrive != nullptr) {  // (null: the caller publishes later, for all slots at once)
     __syncwarp();
     if (lane == 0) {
       if (wrote_rows) __threadfence();

@@ -565,7 +565,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     P.peer_col = g.rank * n_heads;
     unsigned* ctl = static_cast<unsigned*>(g.control);
     P.seq = ctl + gather_seq_offset(g.slots, g.world) + g.slot;
-    P.arrive = reinterpret_cast<unsigned long long*>(ctl + gather_arrive_offset(g.slots, g.world)) + g.slot;
+    P.arrive = (flags & FQB_GATHER_PUBLISH_LATER)
+                   ? nullptr
+                   : reinterpret_cast<unsigned long long*>(ctl + gather_arrive_offset(g.slots, g.world)) + g.slot;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -725,6 +727,26 @@ int fqb_gather_wait_all(const fqb_gather* g, void* stream) {
   const unsigned long long limit_ns = static_cast<unsigned long long>(g->timeout_ms > 0 ? g->timeout_ms : 1000) * 1000000ull;
   FQB_CUDA_TRY(launch_ex(gather_wait_all_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), true, ctl,
                          ctl + gather_seq_offset(g->slots, g->world), g->slots, g->world, limit_ns));
+  return FQB_OK;
+}
+
+int fqb_gather_publish_all(const fqb_gather* g, void* stream) {
+  if (!g || !g->control || g->world < 1 || g->world > kMaxPeers || g->rank < 0 || g->rank >= g->world || g->slots < 1)
+    return set_error(FQB_ERR_INVALID, "gather_publish_all: bad reassembly descriptor");
+  PublishAllParams P;
+  unsigned* ctl = static_cast<unsigned*>(g->control);
+  P.seq = ctl + gather_seq_offset(g->slots, g->world);
+  for (int r = 0; r < kMaxPeers; ++r) P.flags[r] = nullptr;
+  for (int r = 0; r < g->world; ++r) {
+    if (!g->flags[r]) return set_error(FQB_ERR_INVALID, "gather_publish_all: control block of rank %d missing", r);
+    P.flags[r] = static_cast<unsigned*>(g->flags[r]);
+  }
+  P.slots = g->slots;
+  P.world = g->world;
+  P.rank = g->rank;
+  // a plain launch: it starts when every earlier kernel of the stream has completed
+  gather_publish_all_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  FQB_CUDA_TRY(cudaGetLastError());
   return FQB_OK;
 }
 

@@ -83,6 +83,7 @@ def attn_decode_planned(q, q_stride, cache_kv, num_blocks, out, n_heads, n_kv, h
 
 
 DECODE_HISTORY_STABLE = 2
+GATHER_PUBLISH_LATER = 4
 
 
 def append_attn_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos,
@@ -117,6 +118,12 @@ def gather_wait(gather, stream=None):
 def gather_wait_all(gather, stream=None):
     """fqb_gather_wait_all: the same wait over every slot of the control block."""
     check(lib.fqb_gather_wait_all(C.addressof(gather), _stream(stream)), "fqb_gather_wait_all")
+
+
+def gather_publish_all(gather, stream=None):
+    """fqb_gather_publish_all: publishes every slot of the control block (after launches made with
+    GATHER_PUBLISH_LATER)."""
+    check(lib.fqb_gather_publish_all(C.addressof(gather), _stream(stream)), "fqb_gather_publish_all")
 
 
 def kv_append_fp8(cache8, scales, num_blocks, kv_heads_local, qkv, src_stride, k_off, v_off, bt, bt_stride, bt_row, pos,

@@ -241,6 +241,16 @@ int fqb_append_attn_decode_gather(void* cache, int num_blocks, int kv_heads_loca
 int fqb_gather_wait(const fqb_gather* gather, void* stream);
 /* The same wait for every slot of the control block in one kernel (end of a step). */
 int fqb_gather_wait_all(const fqb_gather* gather, void* stream);
+/* FQB_GATHER_PUBLISH_LATER (a flag of fqb_append_attn_decode_gather): the kernel still stores every
+ * finished row into all ranks' buffers, but neither counts its warps in nor publishes. A launch that the
+ * next one waits for then ends without a system-wide fence and a round of flag stores over NVLink (about
+ * 15 us per launch where every launch waits for the one before it). The caller publishes all slots at
+ * once with fqb_gather_publish_all after the last such launch of the step: a one-CTA kernel, launched
+ * without overlap, so every earlier kernel of the stream has completed and its stores have been performed
+ * when it bumps each slot's publish counter and stores it into every rank's flag words. All ranks make
+ * the same number of publishes per slot, as with the in-kernel form. */
+#define FQB_GATHER_PUBLISH_LATER 4u
+int fqb_gather_publish_all(const fqb_gather* gather, void* stream);
 int fqb_peer_alloc(int64_t bytes, void** ptr /* host: receives a zeroed device allocation */);
 int fqb_peer_free(void* ptr);
 int fqb_peer_export(void* ptr, void* handle64 /* host, FQB_PEER_HANDLE_BYTES */);

@@ -73,6 +73,65 @@ def test_every_rank_receives_the_full_rows(world, flags):
         m.free()
 
 
+@pytest.mark.parametrize("world,flags", [(2, 2), (4, 0), (8, 1)])
+def test_rows_stored_by_the_kernel_and_published_later_for_all_slots(world, flags):
+    """FQB_GATHER_PUBLISH_LATER: three "layers" (slots) per rank store their rows into every rank's buffers
+    without publishing; a wait before the publish gives up; fqb_gather_publish_all then announces all
+    slots at once and the waits return, twice in a row (publish numbers 1 and 2)."""
+    lengths = [300, 17, 1200, 64, 5]
+    n, kvl, slots = len(lengths), 8 // world, 3
+    c = synth.decode_case(lengths, 120, seed=870 + world, n_kv=8, shuffle_rids=True)
+    before = c.cache.copy()
+    for s, L in enumerate(lengths):
+        before[c.tables[s][(L - 1) // 16], :, (L - 1) % 16] = 0x7FC0
+    after = before.copy()
+    O.kv_append(after, c.qkv, c.q_stride, 4096, 5120, c.bt, c.req, c.pos)
+    c.cache = after
+    want = O.attn_decode(c.qkv, c.q_stride, after, 32, 8, c.pos, c.qstart, c.decode_rids, c.bt, c.scale, rows=n)
+    row_bytes = n * 32 * 128 * 2
+    mems = [peer.PeerMemory(slots * row_bytes, slots, world) for _ in range(world)]
+    direct = [(m.buf, m.ctl) for m in mems]
+    groups = [peer.PeerGroup(r, world, mems[r], direct=direct) for r in range(world)]
+    qkv = dv(c.qkv)
+    meta = (dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt))
+    shards = [dv(np.ascontiguousarray(before[..., r * kvl * 128:(r + 1) * kvl * 128])) for r in range(world)]
+    outs = [torch.empty((n, kvl * 4 * 128), dtype=torch.int16, device=DEV) for _ in range(world)]
+    scr = [Scratch(n, kvl * 4, c.max_blocks) for _ in range(world)]
+    for rnd in range(2):
+        for m in mems:
+            m.as_tensor(DEV).fill_(0x7FC0)
+        for slot in range(slots):
+            for r in range(world):
+                d = groups[r].desc(slot=slot, byte_offset=slot * row_bytes, timeout_ms=50)
+                fq.append_attn_decode_gather(shards[r], c.num_blocks, kvl, qkv, c.q_stride, r * kvl * 4 * 128,
+                                             4096 + r * kvl * 128, 5120 + r * kvl * 128, outs[r], 128, meta[0], meta[1],
+                                             meta[2], None, n, meta[3], c.max_blocks, 16, c.scale, scr[r].pm, scr[r].pl,
+                                             scr[r].pa, scr[r].slots, d, flags=flags | fq.GATHER_PUBLISH_LATER)
+        if rnd == 0 and world == 2:   # nothing has been announced yet: a wait runs out
+            fq.gather_publish_all(groups[0].desc(slot=0))   # rank 0 alone
+            fq.gather_wait(groups[0].desc(slot=2, timeout_ms=50))
+            torch.cuda.synchronize()
+            code, detail = fq.device_status(raise_on_error=False)
+            assert code == -5 and detail[1] == 7, (code, detail)   # FQB_ERR_TIMEOUT from the gather wait kernel
+            fq.device_status_reset()
+            fq.gather_publish_all(groups[1].desc(slot=0))
+        else:
+            for r in range(world):
+                fq.gather_publish_all(groups[r].desc(slot=0))
+        for r in range(world):
+            fq.gather_wait_all(groups[r].desc(slot=0, timeout_ms=2000))
+        torch.cuda.synchronize()
+        fq.device_status()
+        for r in range(world):
+            full = host(mems[r].as_tensor(DEV).view(slots, n, 32 * 128).clone())
+            for slot in range(slots):
+                assert maxabs(full[slot], want) <= TOL, (rnd, r, slot)
+    for g in groups:
+        g.close()
+    for m in mems:
+        m.free()
+
+
 def test_a_wait_whose_peers_never_publish_gives_up_with_a_status():
     """Rank 0 of a 2-rank group publishes; nobody plays rank 1. The wait returns after its limit, the
     context stays usable and the status names the gather kernel and the silent rank."""
