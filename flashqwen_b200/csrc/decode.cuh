@@ -58,6 +58,7 @@ struct DecodeParams {
   int kvh_base;    // first kv head this launch serves (launches cover 8, 4, 2 or 1 heads each)
   int mode;        // kDecodeWaitFirst / kDecodeNoWait / kDecodeWaitRows, see below
   int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
+  int end_weight;  // what a sequence end inside a segment is charged, in pages, when the page list is cut
   const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
   const float* scales;  // fp8 cache only: [num_blocks][n_kv][2 planes][16 tokens] fp32
   // fused append of the new token (cache_w == nullptr: none). The rows are qkv + flat * q_stride
@@ -448,10 +449,30 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   const int total_pages = s_cum[n_decode];
   const int nseg = static_cast<int>(gridDim.x) * SUB;
   const int seg = static_cast<int>(blockIdx.x) * SUB + sub;
-  const int W = max(2, (total_pages + nseg - 1) / nseg);  // pages per segment
-  const long long lo_ll = static_cast<long long>(seg) * W;
-  const int lo = lo_ll < total_pages ? static_cast<int>(lo_ll) : total_pages;
-  const int hi = min(total_pages, lo + W);
+  // The list is cut into segments of equal COST, not of equal length: a sequence that ends inside a
+  // segment costs its warp a fixed amount on top of its pages (the row or partial to write, one more
+  // ticket and possibly a merge at the end, a new set of q rows), and with equal lengths the launch
+  // ends with the warps that have several such ends. So position x of the weighted list is page
+  // x - end_weight * (sequences before it), each sequence is followed by end_weight positions that
+  // hold no page, and segment s covers positions [s W, (s+1) W).
+  const int w_end = P.end_weight;
+  const long long total_w = total_pages + static_cast<long long>(w_end) * n_decode;
+  const int W = max(2, static_cast<int>((total_w + nseg - 1) / nseg));  // positions per segment
+  auto page_at = [&](long long x) {  // the first page at or after weighted position x
+    if (x >= total_w) return total_pages;
+    int a = 0, b = n_decode;  // largest a with s_cum[a] + w_end * a <= x
+    while (b - a > 1) {
+      const int mid = (a + b) >> 1;
+      if (s_cum[mid] + static_cast<long long>(w_end) * mid <= x) a = mid; else b = mid;
+    }
+    const int o = static_cast<int>(x - (s_cum[a] + static_cast<long long>(w_end) * a));
+    return s_cum[a] + min(o, s_cum[a + 1] - s_cum[a]);
+  };
+  auto segment_of = [&](int di, int page_in_seq) {
+    return static_cast<int>((s_cum[di] + static_cast<long long>(w_end) * di + page_in_seq) / W);
+  };
+  const int lo = page_at(static_cast<long long>(seg) * W);
+  const int hi = page_at(static_cast<long long>(seg + 1) * W);
   unsigned long long* counters =
       reinterpret_cast<unsigned long long*>(P.pl + decode_counter_base(P.partial_slots, n_decode * P.n_kv));
 
@@ -580,9 +601,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     int di_mine = -1, b0 = 0, b1 = 0, last = 0;
     if (lane < n_pend) {
       di_mine = s_pend[lane];
-      const int first = s_cum[di_mine], np_seq = s_cum[di_mine + 1] - first;
-      b0 = first / W;
-      b1 = (first + np_seq - 1) / W;
+      const int np_seq = s_cum[di_mine + 1] - s_cum[di_mine];
+      b0 = segment_of(di_mine, 0);
+      b1 = segment_of(di_mine, np_seq - 1);
       unsigned long long* c = counters + static_cast<long long>(di_mine) * P.n_kv + kvh;
       __threadfence();
       last = take_ticket_is_last(c, P.epoch, b1 - b0 + 1) ? 1 : 0;
