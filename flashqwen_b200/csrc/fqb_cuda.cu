@@ -180,14 +180,16 @@ using DecodeCfg8 = DecodeCfg<8, 3, 8, 1, 512>;
 using DecodeCfg4 = DecodeCfg<4, 3, 4, 2, 256>;
 using DecodeCfg2 = DecodeCfg<4, 3, 2, 2, 256>;
 using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
-// The 1-head shape of launches that wait for nothing: two warps per CTA and four launches resident per
-// SM instead of four warps and two. A launch then cuts the page list into half as many segments, so a
-// warp's fixed costs (block-table and TMA round trips before its first page, partial, ticket and merge
-// after its last) are spread over twice the pages, and four launches at different stages hide them
-// better than two: 11.3 instead of 12.3 us per launch of 68.6 MB (one of 8 kv heads, 64 sequences).
-// Shapes with one warp per CTA (8 or 6 resident) measured 12.0-12.1 us; the same change for the 2-head
-// shape measured no difference, and the 4-head shape has no room for a third resident CTA's registers.
-using DecodeCfg1I = DecodeCfg<2, 3, 1, 4, 256>;
+// The 1-head shape of launches that wait for nothing: two warps per CTA with rings of 2 and six
+// launches resident per SM instead of four warps with rings of 3 and two launches. A launch then cuts the
+// page list into half as many segments, so a warp's fixed costs (block-table and TMA round trips before
+// its first page, partial, ticket and merge after its last) are spread over twice the pages, and six
+// launches at different stages hide them better than two: 11.4 instead of 12.3 us per launch of 68.6 MB
+// (one of 8 kv heads, 64 sequences). Rings of 3 with four resident launches measured 11.6 on the same
+// GPU, eight resident launches 12.7, three warps per CTA 12.0 (four resident) and 14.6 (three), one warp
+// per CTA 12.0-12.1; the same change for the 2-head shape measured no difference, and the 4-head shape
+// loses more in the launches that wait (rings of 2) than it gains.
+using DecodeCfg1I = DecodeCfg<2, 2, 1, 6, 256>;
 // fp8 cache: slices are half the size, so the rings are twice as deep for the same bytes in flight
 using Decode8Cfg8 = DecodeCfg<8, 6, 8, 1, 512>;
 using Decode8Cfg4 = DecodeCfg<4, 6, 4, 2, 256>;
