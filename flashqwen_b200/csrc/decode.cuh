@@ -6,10 +6,11 @@
 // 0..qpos inclusive, one kv head serves its 4 query heads, fp32 accumulation, bf16 output at
 // out[(flat*n_heads + h)*128 + d]. The design is not the reference's:
 //
-//   * Work is the flat list of pages of all sequences (sequence-major). It is cut into equal
-//     contiguous SEGMENTS, one per (CTA, warp group) of a persistent grid, on the device from the
-//     actual context lengths -- the grid depends only on the SM count, so the launch can sit in a
-//     CUDA graph while lengths change. Warp w serves kv head w % HEADS of segment
+//   * Work is the flat list of pages of all sequences (sequence-major). It is cut into contiguous
+//     SEGMENTS of equal cost (a page counts 1, a sequence end inside the segment a few pages), one
+//     per (CTA, warp group) of a persistent grid, on the device from the actual context lengths --
+//     the grid depends only on the SM count, so the launch can sit in a CUDA graph while lengths
+//     change. Warp w serves kv head w % HEADS of segment
 //     blockIdx.x * SUB + w / HEADS: with all local heads in one CTA (HEADS == NW) the loads a CTA has
 //     in flight cover whole 64 KiB pages (all heads of K and V are adjacent in memory); with one or
 //     two local heads the SUB warps that share a head take neighbouring segments.

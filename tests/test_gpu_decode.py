@@ -427,3 +427,16 @@ def test_long_page_lists_fused_and_replayed(flags, n_kv, lengths):
         torch.cuda.synchronize()
         fq.device_status()
         assert maxabs(host(out), want) <= TOL
+
+
+@pytest.mark.parametrize("n_kv", [8, 1])
+@pytest.mark.parametrize("lengths", [[1 + (7 * i) % 20 for i in range(256)],
+                                     [9000] + [1 + i % 3 for i in range(200)],
+                                     [16] * 130 + [17] * 100, [5000, 5000]])
+def test_segments_of_equal_cost_with_many_or_few_sequence_ends(n_kv, lengths):
+    """The page list is cut by cost (pages + a charge per sequence end). Many one-page sequences make the
+    charges outweigh the pages (segments hold a handful of pages, some none); one long sequence beside
+    many tiny ones puts most ends into a few segments; two long sequences have almost none."""
+    blocks = sum((L + 15) // 16 for L in lengths) + 4
+    c = synth.decode_case(lengths, blocks, seed=900 + n_kv + len(lengths), n_kv=n_kv, shuffle_rids=True)
+    assert maxabs(run_decode(c), oracle_decode(c)) <= TOL
