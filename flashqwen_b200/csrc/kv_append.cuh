@@ -112,7 +112,7 @@ struct NormRopeParams {
 // partners are lane-local and the xor-shuffle butterfly below adds squares in the order
 // (t, t+64), then strides 32, 16, 8, 4, 2, 1 -- the reference's shared-memory halving tree --
 // so an IEEE evaluation is reproducible on the host bit for bit.
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256)
 norm_rope_append_kernel(const NormRopeParams P) {
   const int m = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,77 +135,48 @@ norm_rope_append_kernel(const NormRopeParams P) {
   const float2 sn = ok ? __ldg(reinterpret_cast<const float2*>(P.sin_tab + static_cast<long long>(p) * 64) + lane)
                        : make_float2(0.f, 0.f);
   const int nheads = P.q_heads + P.kv_heads;
-  // The V rows of the token (copied as they are) are fetched first and stored last, so that their latency
-  // runs under the norm work.
-  const int vecs = store && ok ? P.a.row_elems / 8 : 0;
+  for (int hd = warp; hd < nheads; hd += 8) {
+    const bool is_k = hd >= P.q_heads;
+    __nv_bfloat16* v = row + (is_k ? P.a.k_off + (hd - P.q_heads) * kHd : P.q_off + hd * kHd);
+    const float* w = is_k ? P.wk : P.wq;
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(v + 2 * lane);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(v + 64 + 2 * lane);
+    const float x0 = __low2float(lo), x1 = __high2float(lo);
+    const float x2 = __low2float(hi), x3 = __high2float(hi);
+    float s0 = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x2, x2));  // dims t, t+64
+    float s1 = __fadd_rn(__fmul_rn(x1, x1), __fmul_rn(x3, x3));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o));
+      s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o));
+    }
+    const float ss = __fadd_rn(s0, s1);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(kHd)), P.eps)));
+    const float2 w_lo = __ldg(reinterpret_cast<const float2*>(w) + lane);
+    const float2 w_hi = __ldg(reinterpret_cast<const float2*>(w + 64) + lane);
+    const float y0 = __fmul_rn(__fmul_rn(x0, inv), w_lo.x), y1 = __fmul_rn(__fmul_rn(x1, inv), w_lo.y);
+    const float y2 = __fmul_rn(__fmul_rn(x2, inv), w_hi.x), y3 = __fmul_rn(__fmul_rn(x3, inv), w_hi.y);
+    const float r0 = __fsub_rn(__fmul_rn(y0, cs.x), __fmul_rn(y2, sn.x));
+    const float r1 = __fsub_rn(__fmul_rn(y1, cs.y), __fmul_rn(y3, sn.y));
+    const float r2 = __fadd_rn(__fmul_rn(y2, cs.x), __fmul_rn(y0, sn.x));
+    const float r3 = __fadd_rn(__fmul_rn(y3, cs.y), __fmul_rn(y1, sn.y));
+    const __nv_bfloat162 out_lo = __floats2bfloat162_rn(r0, r1), out_hi = __floats2bfloat162_rn(r2, r3);
+    if (ok) {
+      *reinterpret_cast<__nv_bfloat162*>(v + 2 * lane) = out_lo;
+      *reinterpret_cast<__nv_bfloat162*>(v + 64 + 2 * lane) = out_hi;
+      if (is_k && store) {
+        __nv_bfloat16* c = P.a.cache + dst + (hd - P.q_heads) * kHd;
+        *reinterpret_cast<__nv_bfloat162*>(c + 2 * lane) = out_lo;
+        *reinterpret_cast<__nv_bfloat162*>(c + 64 + 2 * lane) = out_hi;
+      }
+    }
+  }
+  if (!ok || !store) return;
+  const int vecs = P.a.row_elems / 8;
   const long long plane = static_cast<long long>(kTok) * P.a.row_elems;
-  uint4 vrow = make_uint4(0, 0, 0, 0);
-  const bool one_vec = vecs <= static_cast<int>(blockDim.x);
-  if (one_vec && static_cast<int>(threadIdx.x) < vecs)
-    vrow = __ldg(reinterpret_cast<const uint4*>(row + P.a.v_off) + threadIdx.x);
-  const float2 wq_lo = __ldg(reinterpret_cast<const float2*>(P.wq) + lane);
-  const float2 wq_hi = __ldg(reinterpret_cast<const float2*>(P.wq + 64) + lane);
-  const float2 wk_lo = __ldg(reinterpret_cast<const float2*>(P.wk) + lane);
-  const float2 wk_hi = __ldg(reinterpret_cast<const float2*>(P.wk + 64) + lane);
-  // The row is normalised in place, so the compiler must keep every load of an iteration behind the
-  // stores of the one before it; a warp therefore first loads all the heads it serves in this pass (five
-  // for 32 + 8 heads) and only then starts to write: one memory round trip per pass instead of one per head.
-  constexpr int kBatch = 5;
-  for (int base = warp; base < nheads; base += 8 * kBatch) {
-    __nv_bfloat162 in_lo[kBatch], in_hi[kBatch];
-#pragma unroll
-    for (int k = 0; k < kBatch; ++k) {
-      const int hd = base + 8 * k;
-      if (hd < nheads) {
-        const bool is_k = hd >= P.q_heads;
-        const __nv_bfloat16* v = row + (is_k ? P.a.k_off + (hd - P.q_heads) * kHd : P.q_off + hd * kHd);
-        in_lo[k] = *reinterpret_cast<const __nv_bfloat162*>(v + 2 * lane);
-        in_hi[k] = *reinterpret_cast<const __nv_bfloat162*>(v + 64 + 2 * lane);
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < kBatch; ++k) {
-      const int hd = base + 8 * k;
-      if (hd >= nheads) break;
-      const bool is_k = hd >= P.q_heads;
-      __nv_bfloat16* v = row + (is_k ? P.a.k_off + (hd - P.q_heads) * kHd : P.q_off + hd * kHd);
-      const float x0 = __low2float(in_lo[k]), x1 = __high2float(in_lo[k]);
-      const float x2 = __low2float(in_hi[k]), x3 = __high2float(in_hi[k]);
-      float s0 = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x2, x2));  // dims t, t+64
-      float s1 = __fadd_rn(__fmul_rn(x1, x1), __fmul_rn(x3, x3));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o));
-        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o));
-      }
-      const float ss = __fadd_rn(s0, s1);
-      const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(kHd)), P.eps)));
-      const float2 w_lo = is_k ? wk_lo : wq_lo, w_hi = is_k ? wk_hi : wq_hi;
-      const float y0 = __fmul_rn(__fmul_rn(x0, inv), w_lo.x), y1 = __fmul_rn(__fmul_rn(x1, inv), w_lo.y);
-      const float y2 = __fmul_rn(__fmul_rn(x2, inv), w_hi.x), y3 = __fmul_rn(__fmul_rn(x3, inv), w_hi.y);
-      const float r0 = __fsub_rn(__fmul_rn(y0, cs.x), __fmul_rn(y2, sn.x));
-      const float r1 = __fsub_rn(__fmul_rn(y1, cs.y), __fmul_rn(y3, sn.y));
-      const float r2 = __fadd_rn(__fmul_rn(y2, cs.x), __fmul_rn(y0, sn.x));
-      const float r3 = __fadd_rn(__fmul_rn(y3, cs.y), __fmul_rn(y1, sn.y));
-      const __nv_bfloat162 out_lo = __floats2bfloat162_rn(r0, r1), out_hi = __floats2bfloat162_rn(r2, r3);
-      if (ok) {
-        *reinterpret_cast<__nv_bfloat162*>(v + 2 * lane) = out_lo;
-        *reinterpret_cast<__nv_bfloat162*>(v + 64 + 2 * lane) = out_hi;
-        if (is_k && store) {
-          __nv_bfloat16* c = P.a.cache + dst + (hd - P.q_heads) * kHd;
-          *reinterpret_cast<__nv_bfloat162*>(c + 2 * lane) = out_lo;
-          *reinterpret_cast<__nv_bfloat162*>(c + 64 + 2 * lane) = out_hi;
-        }
-      }
-    }
-  }
-  if (vecs == 0) return;
-  if (one_vec) {
-    if (static_cast<int>(threadIdx.x) < vecs) *(reinterpret_cast<uint4*>(P.a.cache + dst + plane) + threadIdx.x) = vrow;
-  } else {
-    for (int i = threadIdx.x; i < vecs; i += blockDim.x)
-      *(reinterpret_cast<uint4*>(P.a.cache + dst + plane) + i) = __ldg(reinterpret_cast<const uint4*>(row + P.a.v_off) + i);
-  }
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x)
+    *(reinterpret_cast<uint4*>(P.a.cache + dst + plane) + i) =
+        __ldg(reinterpret_cast<const uint4*>(row + P.a.v_off) + i);
 }
 
 }  // namespace fqb
