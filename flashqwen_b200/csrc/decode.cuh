@@ -908,17 +908,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
     }
   }
   // ---- reassembly: tell every rank that this rank's rows of the launch are in its buffer ----
-  // One fence per warp, and only in warps that stored rows: the warp barrier orders the lanes' stores
-  // before lane 0's fence, which is cumulative over them (the pattern of a grid-wide barrier). The fence
-  // is device-scope -- it returns when the stores have been performed, wherever their memory is; the one
-  // system-scope release is the flag store of the launch's last warp. Arrivals are counted per CTA in
-  // shared memory first and then with ONE plain atomic add per CTA on the slot's word (hundreds of warps
-  // in a compare-and-swap loop on one word serialise for tens of microseconds); the last CTA puts the word
-  // back to zero, which is why two launches that can overlap must not share a slot.
+  // Fences are cumulative, so the expensive ones are few: a warp orders its lanes' stores before lane 0
+  // with the warp barrier and hands them to its CTA with a CTA-scope fence and an arrival in shared
+  // memory; the CTA's last warp makes them (and its own) visible to the GPU with ONE device-scope fence
+  // -- that one returns only when the stores have been performed, wherever their memory is -- and arrives
+  // on the slot's word with one plain atomic add (hundreds of warps in a compare-and-swap loop on one word
+  // serialise for tens of microseconds); the launch's last CTA issues the one system-scope fence and then
+  // stores the publish number into every rank's flag word (relaxed: the fence before them orders them
+  // after everything the arrivals have handed over). It also puts the word back to zero, which is why
+  // two launches that can overlap must not share a slot.
   if (P.n_peers > 0 && P.arrive != nullptr) {  // (null: the caller publishes later, for all slots at once)
     __syncwarp();
     if (lane == 0) {
-      if (wrote_rows) __threadfence();
+      if (wrote_rows) __threadfence_block();
       if (atomicAdd(s_arrive, 1u) + 1u == static_cast<unsigned>(NW)) {
         __threadfence();
         unsigned* word = reinterpret_cast<unsigned*>(P.arrive);
@@ -927,7 +929,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           const unsigned v = atomicAdd(P.seq, 1u) + 1u;
           __threadfence_system();
           for (int r = 0; r < P.n_peers; ++r)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flag[r]), "r"(v) : "memory");
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(P.peer_flag[r]), "r"(v) : "memory");
         }
       }
     }
