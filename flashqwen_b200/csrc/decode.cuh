@@ -60,6 +60,7 @@ struct DecodeParams {
   int mode;        // kDecodeWaitFirst / kDecodeNoWait / kDecodeWaitRows, see below
   int sync_first;  // 1: wait for every earlier kernel BEFORE letting the next launch start
   int end_weight;  // what a sequence end inside a segment is charged, in pages, when the page list is cut
+  int groups;      // head groups of the launch: CTA b serves heads kvh_base + (b % groups) * HEADS ... of segment b / groups
   const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
   const float* scales;  // fp8 cache only: [num_blocks][n_kv][2 planes][16 tokens] fp32
   // fused append of the new token (cache_w == nullptr: none). The rows are qkv + flat * q_stride
@@ -372,7 +373,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_decode = P.n_decode;
-  const int kvh = P.kvh_base + warp % HEADS, sub = warp / HEADS;
+  // A launch may cover groups * HEADS heads with CTAs of HEADS heads each (CTA b: group b % groups, CTA
+  // index b / groups within the group), which puts more, smaller CTAs on an SM than one CTA for all heads.
+  const int cta = static_cast<int>(blockIdx.x) / P.groups;
+  const int kvh = P.kvh_base + (static_cast<int>(blockIdx.x) % P.groups) * HEADS + warp % HEADS, sub = warp / HEADS;
 
   // The next kernel on the stream may start its own prologue now. This kernel's prologue reads
   // only the step metadata (rids, qstart, pos, bt), which the kernel before it never writes.
@@ -448,8 +452,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   // From here on the warps of the CTA never meet again: each one streams its own segment.
 
   const int total_pages = s_cum[n_decode];
-  const int nseg = static_cast<int>(gridDim.x) * SUB;
-  const int seg = static_cast<int>(blockIdx.x) * SUB + sub;
+  const int nseg = (static_cast<int>(gridDim.x) / P.groups) * SUB;
+  const int seg = cta * SUB + sub;
   // The list is cut into segments of equal COST, not of equal length: a sequence that ends inside a
   // segment costs its warp a fixed amount on top of its pages (the row or partial to write, one more
   // ticket and possibly a merge at the end, a new set of q rows), and with equal lengths the launch

@@ -191,7 +191,6 @@ using DecodeCfg1 = DecodeCfg<4, 3, 1, 2, 256>;
 // loses more in the launches that wait (rings of 2) than it gains.
 using DecodeCfg1I = DecodeCfg<2, 2, 1, 6, 256>;
 // fp8 cache: slices are half the size, so the rings are twice as deep for the same bytes in flight
-using Decode8Cfg8 = DecodeCfg<8, 6, 8, 1, 512>;
 using Decode8Cfg4 = DecodeCfg<4, 6, 4, 2, 256>;
 using Decode8Cfg2 = DecodeCfg<4, 6, 2, 2, 256>;
 using Decode8Cfg1 = DecodeCfg<4, 6, 1, 2, 256>;
@@ -325,11 +324,12 @@ int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n
     FQB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     attr_dev = dev;
   }
-  const int grid = sm_count * ctas_per_sm;
+  int grid = sm_count * ctas_per_sm;
+  grid -= grid % P.groups;  // the same number of CTAs for every head group of the launch
   for (int base = 0; base < n_decode; base += Cfg::MAXD) {
     P.rids = rids + base;
     P.n_decode = n_decode - base < Cfg::MAXD ? n_decode - base : Cfg::MAXD;
-    const long long need = decode_slots_needed(P.n_decode, P.n_kv, grid * Cfg::SUB);
+    const long long need = decode_slots_needed(P.n_decode, P.n_kv, grid / P.groups * Cfg::SUB);
     if (need > P.partial_slots)
       return set_error(FQB_ERR_WORKSPACE, "decode scratch: %lld partial slots needed, %lld given", need,
                        P.partial_slots);
@@ -549,6 +549,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   P.mode = kDecodeWaitFirst;
   P.sync_first = 0;
   P.end_weight = kEndWeightPages;
+  P.groups = 1;
   P.plan = plan;
   P.cache_w = static_cast<__nv_bfloat16*>(cache_w);
   P.k_rel = k_rel;
@@ -628,7 +629,15 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
     const int left = n_kv - base;
     P.kvh_base = base;
     int rc, took;
-    if (left >= 8) { rc = fp8 ? launch_decode<Decode8Cfg8, true>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st) : launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
+    if (left >= 8 && fp8) {
+      // fp8, 8 heads, the launch waits: two head groups of four heads in one launch, three 4-warp CTAs per
+      // SM (12 warps where the 8-head shape has 8; the kernel is bound by its issue rate, see Decode8Cfg4I)
+      P.groups = 2;
+      rc = launch_decode<Decode8Cfg4I, true>(map, P, decode_rids, n_decode, di.sm_count, 3, true, st);
+      P.groups = 1;
+      took = 8;
+    }
+    else if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
     else if (left >= 4) { rc = fp8 ? launch_decode<Decode8Cfg4, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
     else if (left >= 2) { rc = fp8 ? launch_decode<Decode8Cfg2, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
     else { rc = fp8 ? launch_decode<Decode8Cfg1, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
