@@ -108,4 +108,7 @@ def test_reassembly_control_block_layout_and_argument_checks_without_gpu():
     assert _lib.lib.fqb_gather_wait(ctypes.addressof(g), None) == -1
     g.slot, g.control = 0, None
     assert _lib.lib.fqb_gather_wait_all(ctypes.addressof(g), None) == -1
+    assert _lib.lib.fqb_gather_publish_all(ctypes.addressof(g), None) == -1    # no control block
+    g.control, g.rank = 4096, 5                                                 # rank outside the world
+    assert _lib.lib.fqb_gather_publish_all(ctypes.addressof(g), None) == -1
     assert _lib.lib.fqb_peer_export(None, None) == -1 and _lib.lib.fqb_peer_open(None, None) == -1
