@@ -638,6 +638,20 @@ def run_fp8(a, dev, peak, peak_src):
     ms, clocks = event_ms_with_clocks(dev.index or 0, step, max(a.steps, 10), a.warmup)
     fq.device_status()
     assert torch.isfinite(out.float()).all()
+    # reading pages back as bf16 (what a chunked prefill over an fp8 history does first): 2048 pages per call,
+    # walking the layers' pools so that every call is HBM-cold
+    n_dq = min(2048, num_blocks)
+    dq_list = d(np.random.default_rng(a.seed + 9).permutation(num_blocks)[:n_dq].astype(np.int32))
+    stage = torch.empty((n_dq, 2, PAGE, KV_DIM), dtype=torch.bfloat16, device=dev)
+    it_dq = {"i": 0}
+
+    def dequant():
+        it_dq["i"] = (it_dq["i"] + 1) % layers
+        fq.dequant_blocks_fp8(pools[it_dq["i"]], scales[it_dq["i"]], num_blocks, N_KV, dq_list, n_dq, stage)
+
+    ms_dq = event_ms(dequant, max(a.steps, 10), a.warmup)
+    fq.device_status()
+    dq_bytes = n_dq * (2 * PAGE * KV_DIM * 3 + 2 * PAGE * N_KV * 4)   # bytes in, bf16 out, scales
     sum_ctx = int(sum(lengths))
     nbytes = sum_ctx * (2 * KV_DIM + 2 * N_KV * 4) + a.batch * 2 * Q_DIM * 2   # e4m3 K+V, their scales, q in, out
     gbs = nbytes * layers / (ms * 1e-3) / 1e9
@@ -649,6 +663,9 @@ def run_fp8(a, dev, peak, peak_src):
                        "bytes_per_layer": nbytes, "sum_ctx": sum_ctx,
                        "l2": f"{layers} pools of 0.54 GB walked per step, larger than L2"},
             "clocks": clocks,
+            "dequant_blocks": {"kernel": "dequant_blocks_fp8 (pages read back as bf16)", "pages": n_dq, "ms": round(ms_dq, 4),
+                               "GB/s": round(dq_bytes / (ms_dq * 1e-3) / 1e9, 1), "frac": round(dq_bytes / (ms_dq * 1e-3) / 1e9 / peak, 4),
+                               "bytes": dq_bytes},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                          "traffic": None, "peak_source": peak_src, "launch_us": round(layer_s * 1e6, 2),
                          "algorithmic_bytes_per_launch": nbytes}}

@@ -26,6 +26,7 @@ from .ops import (  # noqa: F401
     copy_blocks,
     copy_blocks_layers,
     decode_partial_slots,
+    dequant_blocks_fp8,
     device_status,
     device_status_reset,
     gather_blocks,

@@ -169,6 +169,14 @@ __device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t four_bytes, uint32_t&
       : "=r"(lo), "=r"(hi)
       : "r"(four_bytes));
 }
+// an f16x2 word as two floats (low half first); exact
+__device__ __forceinline__ float2 f16x2_to_f32x2(uint32_t h) {
+  float2 f;
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(f.x), "=f"(f.y)
+      : "r"(h));
+  return f;
+}
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

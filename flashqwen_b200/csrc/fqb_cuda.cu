@@ -462,6 +462,21 @@ int fqb_kv_append_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_
   return FQB_OK;
 }
 
+int fqb_dequant_blocks_fp8(const void* cache8, const float* scales, int num_blocks, int kv_heads_local,
+                           const int32_t* list, int n, void* out, void* stream) {
+  if (n <= 0) return FQB_OK;
+  if (!cache8 || !scales || !list || !out) return set_error(FQB_ERR_INVALID, "dequant_blocks_fp8: null pointer");
+  if (num_blocks <= 0 || kv_heads_local <= 0) return set_error(FQB_ERR_INVALID, "dequant_blocks_fp8: non-positive size");
+  if (!aligned16(cache8) || !aligned16(scales) || !aligned16(out))
+    return set_error(FQB_ERR_INVALID, "dequant_blocks_fp8: misaligned pointer");
+  if (n > 2147483647 / 2) return set_error(FQB_ERR_SHAPE, "dequant_blocks_fp8: too many blocks");
+  // a block has 32 (plane, token) rows, one per warp: four CTAs of eight warps
+  dequant_blocks_fp8_kernel<<<dim3(n, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(cache8), scales, num_blocks, kv_heads_local, list, static_cast<__nv_bfloat16*>(out));
+  FQB_CUDA_TRY(cudaGetLastError());
+  return FQB_OK;
+}
+
 int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const float* scales, int num_blocks, void* out,
                         int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                         const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,

@@ -97,6 +97,47 @@ kv_append_fp8_kernel(const AppendParams P, float* __restrict__ scales) {
   }
 }
 
+// Blocks of the fp8 cache read back as bf16 into a dense buffer [n][2][16][row_elems]: out block i is
+// block list[i], every value bf16(e4m3_to_float(byte) * scale), the product one fp32 multiplication (so
+// the host restatement gives the same bits). For the chunked prefill of a request whose history lives in
+// the fp8 cache: its pages are read back once per chunk into a staging pool that the prefill kernel
+// attends. One warp per (plane, token) row of the block: a lane turns 16 bytes into 16 bf16 at a time.
+__global__ void __launch_bounds__(256)
+dequant_blocks_fp8_kernel(const uint8_t* __restrict__ cache8, const float* __restrict__ scales, int num_blocks,
+                          int heads, const int* __restrict__ list, __nv_bfloat16* __restrict__ out) {
+  const int i = blockIdx.x;
+  const int blk = __ldg(list + i);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (static_cast<unsigned>(blk) >= static_cast<unsigned>(num_blocks)) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) report(FQB_ERR_INDEX, kKidBlocks, blk);
+    return;
+  }
+  const int row_elems = heads * kHd;
+  const int chunks = row_elems / 16;  // 16-byte chunks of a row; 8 per head
+  for (int r = blockIdx.y * 8 + warp; r < 2 * kTok; r += gridDim.y * 8) {
+    const int pl = r / kTok, t = r % kTok;
+    const long long row = (static_cast<long long>(pl) * kTok + t) * row_elems;
+    const uint8_t* src = cache8 + static_cast<long long>(blk) * 2 * kTok * row_elems + row;
+    __nv_bfloat16* dst = out + static_cast<long long>(i) * 2 * kTok * row_elems + row;
+    for (int c = lane; c < chunks; c += 32) {
+      const float s = __ldg(scales + ((static_cast<long long>(blk) * heads + (c >> 3)) * 2 + pl) * kTok + t);
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(src) + c);
+      const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+      uint32_t o[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint32_t h01, h23;
+        e4m3x4_to_f16x2x2(w[k], h01, h23);
+        const float2 f01 = f16x2_to_f32x2(h01), f23 = f16x2_to_f32x2(h23);
+        o[2 * k] = pack_bf16(__fmul_rn(f01.x, s), __fmul_rn(f01.y, s));
+        o[2 * k + 1] = pack_bf16(__fmul_rn(f23.x, s), __fmul_rn(f23.y, s));
+      }
+      reinterpret_cast<uint4*>(dst)[2 * c] = make_uint4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<uint4*>(dst)[2 * c + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
 struct NormRopeParams {
   AppendParams a;       // a.qkv is written in place, so the pointer is cast back to mutable
   int q_heads, kv_heads;

@@ -134,6 +134,13 @@ def kv_append_fp8(cache8, scales, num_blocks, kv_heads_local, qkv, src_stride, k
           "fqb_kv_append_fp8")
 
 
+def dequant_blocks_fp8(cache8, scales, num_blocks, kv_heads_local, blocks, n, out, stream=None):
+    """fqb_dequant_blocks_fp8: blocks `blocks` (device int32) of the fp8 cache read back as bf16 into the dense
+    pool `out` [n,2,16,kv_heads_local*128]."""
+    check(lib.fqb_dequant_blocks_fp8(_ptr(cache8), _ptr(scales), num_blocks, kv_heads_local, _ptr(blocks), n, _ptr(out),
+                                     _stream(stream)), "fqb_dequant_blocks_fp8")
+
+
 def attn_decode_fp8(q, q_stride, cache8, scales, num_blocks, out, n_heads, n_kv, head_dim, pos, qstart, decode_rids,
                     n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, stream=None, flags=0):
     """fqb_attn_decode_fp8: decode attention over the e4m3 cache."""

@@ -198,6 +198,15 @@ int64_t fqb_kv_scale_bytes_fp8(int num_blocks, int kv_heads_local);
 int fqb_kv_append_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
                       int k_off, int v_off, const int32_t* bt, int bt_stride, const int32_t* bt_row,
                       const int32_t* pos, int M, void* stream);
+/* Blocks of the fp8 cache read back as bf16: out is a dense pool [n][2][16][kv_heads_local*128] bf16 in the
+ * layout of the bf16 cache, out block i = block list[i] (device array), every value
+ * bf16(e4m3_to_float(byte) * scale), reproducible bit for bit on the host. For the chunked prefill of a
+ * request whose history lives in the fp8 cache: read its pages back into a staging pool, append the
+ * chunk's rows to the staging pool with fqb_kv_append (and to the fp8 cache with fqb_kv_append_fp8), and
+ * run fqb_attn_prefill over the staging pool with the block table 0, 1, 2, ... Ids outside
+ * [0, num_blocks) raise FQB_ERR_INDEX in the device status and leave their output block untouched. */
+int fqb_dequant_blocks_fp8(const void* cache8, const float* scales, int num_blocks, int kv_heads_local,
+                           const int32_t* list, int n, void* out, void* stream);
 int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const float* scales, int num_blocks, void* out,
                         int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                         const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,

@@ -153,6 +153,26 @@ void orc_kv_append_fp8(uint8_t* cache8, float* scales, int kv_dim, const uint16_
   }
 }
 
+// Blocks of the fp8 cache read back as bf16 (no reference counterpart; the format is the one of
+// orc_kv_append_fp8): out block i = block list[i], every value bf16(e4m3_to_float(byte) * scale) --
+// the product is one fp32 multiplication, the conversion rounds to nearest even.
+void orc_dequant_blocks_fp8(const uint8_t* cache8, const float* scales, int kv_dim, const int32_t* list, int n,
+                            uint16_t* out) {
+  const int n_kv = kv_dim / kHd;
+  const int64_t plane = static_cast<int64_t>(kTok) * kv_dim;
+  for (int i = 0; i < n; ++i) {
+    const int64_t blk = list[i];
+    for (int pl = 0; pl < 2; ++pl)
+      for (int t = 0; t < kTok; ++t)
+        for (int h = 0; h < n_kv; ++h) {
+          const float s = scales[((blk * n_kv + h) * 2 + pl) * kTok + t];
+          const uint8_t* src = cache8 + (blk * kPlanes + pl) * plane + static_cast<int64_t>(t) * kv_dim + h * kHd;
+          uint16_t* dst = out + (static_cast<int64_t>(i) * kPlanes + pl) * plane + static_cast<int64_t>(t) * kv_dim + h * kHd;
+          for (int d = 0; d < kHd; ++d) dst[d] = f2bf(e4m3_to_f32(src[d]) * s);
+        }
+  }
+}
+
 // Decode attention over the fp8 cache: orc_attn_decode with every K / V value read back as
 // e4m3_to_float(byte) * scale (exact in fp32: 4 significant bits times a float).
 void orc_attn_decode_fp8(const uint16_t* q, int q_stride, const uint8_t* cache8, const float* scales,

@@ -91,6 +91,14 @@ def kv_append_fp8(cache8, scales, qkv, src_stride, k_off, v_off, bt, bt_row, pos
                           bt.shape[1], _p(bt_row, _pi), _p(pos, _pi), len(pos))
 
 
+def dequant_blocks_fp8(cache8, scales, blocks):
+    """Blocks `blocks` of the fp8 cache as bf16 bit patterns [n,2,16,kv_dim]."""
+    cache8, scales, blocks = _c(cache8, np.uint8), _c(scales, np.float32), _c(blocks, np.int32)
+    out = np.zeros((len(blocks),) + cache8.shape[1:], np.uint16)
+    orc.orc_dequant_blocks_fp8(_p(cache8, _pu8), _p(scales, _pf), cache8.shape[-1], _p(blocks, _pi), len(blocks), _p(out, _pu16))
+    return out
+
+
 def attn_decode_fp8(q, q_stride, cache8, scales, n_heads, n_kv, pos, qstart, decode_rids, bt, scale, rows, nthreads=8):
     q, cache8, scales = _c(q, np.uint16), _c(cache8, np.uint8), _c(scales, np.float32)
     pos, qstart, rids, bt = _c(pos, np.int32), _c(qstart, np.int32), _c(decode_rids, np.int32), _c(bt, np.int32)

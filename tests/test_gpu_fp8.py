@@ -142,3 +142,76 @@ def test_config2_shape_and_distance_to_the_unquantised_result():
     O.kv_append(cache16, c.rows, 2048, 0, 1024, c.bt, c.req, c.row_pos)
     ref16 = O.attn_decode(c.qkv, c.q_stride, cache16, 32, 8, c.pos, c.qstart, c.decode_rids, c.bt, c.scale, rows=64)
     assert maxabs(got, ref16) <= 0.15
+
+
+def _same_bits_or_both_nan(got, want):
+    g, w = synth.bf16_to_f32(got), synth.bf16_to_f32(want)
+    nan = np.isnan(w)
+    return np.array_equal(np.isnan(g), nan) and np.array_equal(got[~nan], want[~nan])
+
+
+@pytest.mark.parametrize("n_kv", [8, 2, 1])
+def test_blocks_read_back_as_bf16_bit_for_bit(n_kv):
+    """fqb_dequant_blocks_fp8 against the oracle: every written value bit for bit (one fp32 product, one
+    rounding to bf16), never-written slots (NaN bytes and scales) come back as NaN; an id outside the pool is
+    reported and its output block left alone."""
+    lengths = [70, 16, 1, 333, 48]
+    rs = np.asarray([1.0, 1e-3, 300.0, 0.0] * 117, np.float32)[:sum(lengths)]
+    c = build(lengths, 40, seed=31 + n_kv, n_kv=n_kv, extra_scale=rs)
+    cache8, scales = device_append(c)
+    used = np.unique(c.bt[c.bt >= 0]) if (c.bt < 0).any() else np.unique(c.bt)
+    rng = np.random.default_rng(5)
+    blocks = np.concatenate([rng.permutation(used), used[:3]]).astype(np.int32)
+    out = torch.full((len(blocks), 2, 16, n_kv * 128), 0x1234, dtype=torch.int16, device=DEV)
+    fq.dequant_blocks_fp8(cache8, scales, c.num_blocks, n_kv, dv(blocks), len(blocks), out)
+    torch.cuda.synchronize()
+    fq.device_status()
+    assert _same_bits_or_both_nan(host(out), O.dequant_blocks_fp8(c.cache8, c.scales, blocks))
+    bad = np.asarray([int(used[0]), c.num_blocks + 7], np.int32)
+    out2 = torch.full((2, 2, 16, n_kv * 128), 0x1234, dtype=torch.int16, device=DEV)
+    fq.dequant_blocks_fp8(cache8, scales, c.num_blocks, n_kv, dv(bad), 2, out2)
+    torch.cuda.synchronize()
+    code, detail = fq.device_status(raise_on_error=False)
+    assert code == -6 and detail[3] == c.num_blocks + 7, (code, detail)   # FQB_ERR_INDEX, the id
+    fq.device_status_reset()
+    assert (host(out2)[1] == 0x1234).all()
+
+
+@pytest.mark.parametrize("hist,chunk", [(0, 40), (100, 60), (1000, 130)])
+def test_chunked_prefill_over_a_history_kept_in_the_fp8_cache(hist, chunk):
+    """The recipe of include/fqb.h: the request's pages are read back from the fp8 cache into a bf16 staging
+    pool, the chunk's rows are appended to the staging pool, and fqb_attn_prefill attends the staging pool
+    with the block table 0, 1, 2, ... -- against the oracle doing the same on the host."""
+    n_kv, kv_dim, q_dim = 2, 256, 1024
+    stride = q_dim + 2 * kv_dim
+    rng = np.random.default_rng(hist + chunk)
+    n_stage = (hist + chunk + 15) // 16
+    c = build([max(hist, 1)], n_stage + 5, seed=77 + hist, n_kv=n_kv)
+    cache8, scales = device_append(c)
+    hist_blocks = np.asarray(c.bt[0][:(hist + 15) // 16], np.int32) if hist else np.zeros(0, np.int32)
+    q = synth.unit_rms(rng.standard_normal((chunk, 8, 128), dtype=np.float32)).reshape(chunk, q_dim)
+    k = synth.unit_rms(rng.standard_normal((chunk, n_kv, 128), dtype=np.float32)).reshape(chunk, kv_dim)
+    v = rng.standard_normal((chunk, kv_dim), dtype=np.float32)
+    qkv = synth.f32_to_bf16(np.concatenate([q, k, v], 1))
+    pos = (hist + np.arange(chunk)).astype(np.int32)
+    req, bt = np.zeros(chunk, np.int32), np.arange(n_stage, dtype=np.int32)[None, :]
+    qstart, qlen, rids = np.zeros(1, np.int32), np.asarray([chunk], np.int32), np.zeros(1, np.int32)
+    # host
+    stage_h = np.full((n_stage, 2, 16, kv_dim), 0x7FC0, np.uint16)
+    if hist:
+        stage_h[:len(hist_blocks)] = O.dequant_blocks_fp8(c.cache8, c.scales, hist_blocks)
+    O.kv_append(stage_h, qkv, stride, q_dim, q_dim + kv_dim, bt, req, pos)
+    want = O.attn_prefill(qkv, stride, stage_h, 8, n_kv, pos, qstart, qlen, rids, bt, c.scale, rows=chunk)
+    # device
+    stage = torch.full((n_stage, 2, 16, kv_dim), 0x7FC0, dtype=torch.int16, device=DEV)
+    if hist:
+        fq.dequant_blocks_fp8(cache8, scales, c.num_blocks, n_kv, dv(hist_blocks), len(hist_blocks), stage)
+    dq, dbt, dpos = dv(qkv), dv(bt), dv(pos)
+    fq.kv_append(stage, n_stage, n_kv, dq, stride, q_dim, q_dim + kv_dim, dbt, n_stage, dv(req), dpos, chunk)
+    out = torch.full((chunk, q_dim), 0x7FC0, dtype=torch.int16, device=DEV)
+    fq.attn_prefill(dq, stride, stage, n_stage, out, 8, n_kv, 128, dpos, dv(qstart), dv(qlen), dv(rids), 1, chunk, dbt,
+                    n_stage, 16, c.scale)
+    torch.cuda.synchronize()
+    fq.device_status()
+    assert _same_bits_or_both_nan(host(stage), stage_h)
+    assert maxabs(host(out), want) <= TOL
