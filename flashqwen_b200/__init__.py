@@ -16,6 +16,7 @@ from .ops import (  # noqa: F401
     GATHER_PUBLISH_LATER,
     KvStore,
     append_attn_decode,
+    append_attn_decode_fp8,
     append_attn_decode_gather,
     attn_decode,
     attn_decode_fp8,

@@ -71,6 +71,8 @@ SIGNATURES = {
     "fqb_kv_pool_bytes_fp8": (_i64, [_i, _i]),
     "fqb_kv_scale_bytes_fp8": (_i64, [_i, _i]),
     "fqb_kv_append_fp8": (_i, [_p, _p, _i, _i, _p, _i, _i, _i, _p, _i, _p, _p, _i, _p]),
+    "fqb_append_attn_decode_fp8": (_i, [_p, _p, _i, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p, _i, _p, _i, _i, _f, _p,
+                                        _p, _p, _i64, C.c_uint, _p]),
     "fqb_dequant_blocks_fp8": (_i, [_p, _p, _i, _i, _p, _i, _p, _p]),
     "fqb_attn_decode_fp8": (_i, [_p, _i, _p, _p, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p, _i, _i, _f, _p, _p, _p, _i64,
                                  C.c_uint, _p]),

@@ -32,6 +32,8 @@
 //     part in the attention without a separate append kernel in front.
 #pragma once
 
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace fqb {
@@ -63,6 +65,7 @@ struct DecodeParams {
   int groups;      // head groups of the launch: CTA b serves heads kvh_base + (b % groups) * HEADS ... of segment b / groups
   const int* plan; // optional step plan {r, flat, qpos, page prefix}[n_decode] + total (decode_plan_kernel)
   const float* scales;  // fp8 cache only: [num_blocks][n_kv][2 planes][16 tokens] fp32
+  float* scales_w;      // fp8 cache with the fused append: the same array, written for the step's token
   // fused append of the new token (cache_w == nullptr: none). The rows are qkv + flat * q_stride
   // seen from q: K of cache head kvh at q + k_rel + kvh*128, V at q + v_rel + kvh*128.
   __nv_bfloat16* cache_w;
@@ -730,10 +733,49 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           mma_bf16(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);
         }
       } else {
+        if (appends) {
+          // The step's token in the fp8 format: lanes 0..15 hold the K row of this head, lanes 16..31 the V
+          // row, 8 values each; one scale per row (amax / 448), bytes e4m3(x * (448 / amax)) -- the
+          // operations of kv_append_fp8_kernel, so the cache gets the same bytes. The row goes to the
+          // cache and into the slice that has just arrived (swizzled like the rest of it), its scale to
+          // the scale array and to the slice's scales.
+          const int slot = qpos & (kTok - 1), plane = lane >> 4, l16 = lane & 15;
+          const uint32_t w[4] = {new_row.x, new_row.y, new_row.z, new_row.w};
+          float x[8];
+          float amax = 0.f;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            x[2 * k] = __uint_as_float(w[k] << 16);
+            x[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            amax = fmaxf(amax, fmaxf(fabsf(x[2 * k]), fabsf(x[2 * k + 1])));
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float sq = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+          const float inv = amax > 0.f ? __fdiv_rn(448.0f, amax) : 0.0f;
+          uint32_t b[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            b[k] = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x[2 * k], inv), __fmul_rn(x[2 * k + 1], inv)),
+                                            __NV_SATFINITE, __NV_E4M3);
+          const uint2 bytes = make_uint2(b[0] | (b[1] << 16), b[2] | (b[3] << 16));
+          if (static_cast<unsigned>(a_blk) < static_cast<unsigned>(P.num_blocks)) {
+            uint8_t* c8 = reinterpret_cast<uint8_t*>(P.cache_w);
+            *reinterpret_cast<uint2*>(c8 + ((static_cast<long long>(a_blk) * FQB_PLANES + plane) * kTok + slot) *
+                                               (static_cast<long long>(P.n_kv) * kHd) + kvh * kHd + l16 * 8) = bytes;
+            if (l16 == 0)
+              P.scales_w[((static_cast<long long>(a_blk) * P.n_kv + kvh) * 2 + plane) * kTok + slot] = sq;
+          }
+          *reinterpret_cast<uint2*>(st + plane * (kPageBytes8 / 2) + slot * 128 + (((l16 >> 1) ^ (slot & 7)) << 4) +
+                                    (l16 & 1) * 8) = bytes;
+          if (l16 == 0) reinterpret_cast<float*>(my_scale + cslot * kScaleBytes8)[plane * kTok + slot] = sq;
+        }
         if (nvalid < kTok) {
           // tail of the sequence's last page was never written: bytes there may decode to NaN
           for (int row = nvalid; row < kTok; ++row)
             if (lane < 8) *reinterpret_cast<uint4*>(st + kPageBytes8 / 2 + row * 128 + (lane << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        if (appends || nvalid < kTok) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
         }

@@ -549,6 +549,7 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
   P.n_heads = n_heads;
   P.n_kv = n_kv;
   P.scales = scales;
+  P.scales_w = cache_w ? const_cast<float*>(scales) : nullptr;  // the fused fp8 append writes the token's scales
   P.pos = pos;
   P.qstart = qstart;
   P.rids = decode_rids;
@@ -699,7 +700,7 @@ static int append_decode(void* cache, int num_blocks, int kv_heads_local, const 
                          int k_off, int v_off, void* out, int head_dim, const int32_t* pos, const int32_t* qstart,
                          const int32_t* decode_rids, const int32_t* plan, int n_decode, const int32_t* bt,
                          int max_blocks, int block_size, float scale, float* pm, float* pl, float* pa,
-                         int64_t partial_slots, unsigned flags, const fqb_gather* gather, void* stream) {
+                         int64_t partial_slots, unsigned flags, const fqb_gather* gather, float* scales, void* stream) {
   if (n_decode <= 0 && !gather) return FQB_OK;
   if (!qkv) return set_error(FQB_ERR_INVALID, "append_attn_decode: null pointer");
   if (!aligned16(qkv) || (src_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8) || q_off < 0 || k_off < 0 || v_off < 0)
@@ -712,7 +713,7 @@ static int append_decode(void* cache, int num_blocks, int kv_heads_local, const 
   const int32_t* m2 = plan ? plan : decode_rids;
   return decode_impl(q, src_stride, cache, num_blocks, out, kv_heads_local * kGroup, kv_heads_local, head_dim, m0, m1, m2,
                      n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags, plan, cache,
-                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, gather, nullptr, stream);
+                     static_cast<long long>(k_off) - q_off, static_cast<long long>(v_off) - q_off, gather, scales, stream);
 }
 
 int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride, int q_off,
@@ -722,7 +723,19 @@ int fqb_append_attn_decode(void* cache, int num_blocks, int kv_heads_local, cons
                            int64_t partial_slots, unsigned flags, void* stream) {
   return append_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos, qstart,
                        decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags,
-                       nullptr, stream);
+                       nullptr, nullptr, stream);
+}
+
+int fqb_append_attn_decode_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_local, const void* qkv,
+                               int src_stride, int q_off, int k_off, int v_off, void* out, int head_dim,
+                               const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids, const int32_t* plan,
+                               int n_decode, const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                               float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream) {
+  if (n_decode <= 0) return FQB_OK;
+  if (!scales) return set_error(FQB_ERR_INVALID, "append_attn_decode_fp8: null pointer");
+  return append_decode(cache8, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos, qstart,
+                       decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags,
+                       nullptr, scales, stream);
 }
 
 int fqb_append_attn_decode_gather(void* cache, int num_blocks, int kv_heads_local, const void* qkv, int src_stride,
@@ -734,7 +747,7 @@ int fqb_append_attn_decode_gather(void* cache, int num_blocks, int kv_heads_loca
   if (!gather) return set_error(FQB_ERR_INVALID, "append_attn_decode_gather: null reassembly descriptor");
   return append_decode(cache, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim, pos, qstart,
                        decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa, partial_slots, flags,
-                       gather, stream);
+                       gather, nullptr, stream);
 }
 
 int64_t fqb_gather_control_bytes(int slots, int world) {

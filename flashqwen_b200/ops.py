@@ -134,6 +134,16 @@ def kv_append_fp8(cache8, scales, num_blocks, kv_heads_local, qkv, src_stride, k
           "fqb_kv_append_fp8")
 
 
+def append_attn_decode_fp8(cache8, scales, num_blocks, kv_heads_local, qkv, src_stride, q_off, k_off, v_off, out, head_dim,
+                           pos, qstart, decode_rids, plan, n_decode, bt, max_blocks, block_size, scale, pm, pl, pa,
+                           partial_slots, stream=None, flags=0):
+    """fqb_append_attn_decode_fp8: the fused append + attention call over the fp8 cache."""
+    check(lib.fqb_append_attn_decode_fp8(_ptr(cache8), _ptr(scales), num_blocks, kv_heads_local, _ptr(qkv), src_stride, q_off,
+                                         k_off, v_off, _ptr(out), head_dim, _ptr(pos), _ptr(qstart), _ptr(decode_rids),
+                                         _ptr(plan), n_decode, _ptr(bt), max_blocks, block_size, scale, _ptr(pm), _ptr(pl),
+                                         _ptr(pa), partial_slots, flags, _stream(stream)), "fqb_append_attn_decode_fp8")
+
+
 def dequant_blocks_fp8(cache8, scales, num_blocks, kv_heads_local, blocks, n, out, stream=None):
     """fqb_dequant_blocks_fp8: blocks `blocks` (device int32) of the fp8 cache read back as bf16 into the dense
     pool `out` [n,2,16,kv_heads_local*128]."""

@@ -207,6 +207,14 @@ int fqb_kv_append_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_
  * [0, num_blocks) raise FQB_ERR_INDEX in the device status and leave their output block untouched. */
 int fqb_dequant_blocks_fp8(const void* cache8, const float* scales, int num_blocks, int kv_heads_local,
                            const int32_t* list, int n, void* out, void* stream);
+/* fqb_append_attn_decode over the fp8 cache: the step's token is quantised (the bytes and the scale
+ * fqb_kv_append_fp8 would store) by the warp that streams its page, written to cache8 / scales and attended
+ * in the same kernel; arguments and flags as fqb_append_attn_decode, scales is read and written. */
+int fqb_append_attn_decode_fp8(void* cache8, float* scales, int num_blocks, int kv_heads_local, const void* qkv,
+                               int src_stride, int q_off, int k_off, int v_off, void* out, int head_dim,
+                               const int32_t* pos, const int32_t* qstart, const int32_t* decode_rids, const int32_t* plan,
+                               int n_decode, const int32_t* bt, int max_blocks, int block_size, float scale, float* pm,
+                               float* pl, float* pa, int64_t partial_slots, unsigned flags, void* stream);
 int fqb_attn_decode_fp8(const void* q, int q_stride, const void* cache8, const float* scales, int num_blocks, void* out,
                         int n_heads, int n_kv, int head_dim, const int32_t* pos, const int32_t* qstart,
                         const int32_t* decode_rids, int n_decode, const int32_t* bt, int max_blocks, int block_size,

@@ -215,3 +215,44 @@ def test_chunked_prefill_over_a_history_kept_in_the_fp8_cache(hist, chunk):
     fq.device_status()
     assert _same_bits_or_both_nan(host(stage), stage_h)
     assert maxabs(host(out), want) <= TOL
+
+
+@pytest.mark.parametrize("flags", [0, 1, 2])
+@pytest.mark.parametrize("n_kv", [8, 4, 2, 1])
+def test_fused_append_over_the_fp8_cache(flags, n_kv):
+    """fqb_append_attn_decode_fp8: the cache holds every token but the step's; the call quantises that token
+    (bytes and scale bit for bit what fqb_kv_append_fp8 stores), writes it and attends it. Repeated calls are
+    idempotent; flags 1 / 2 are the launches that wait for nothing / only for the step's rows."""
+    lengths = [1, 15, 16, 17, 33, 100, 257, 640, 5, 1024, 2, 3000]
+    rs = np.asarray([1.0, 0.01, 0.5, 1.0, 0.0, 0.125] * 1000, np.float32)[:sum(lengths)]   # rows of different size, one all zero
+    c = build(lengths, 340, seed=500 + n_kv, n_kv=n_kv, extra_scale=rs)
+    kv_dim, q_dim = n_kv * 128, n_kv * 4 * 128
+    n = len(lengths)
+    # the fused row of each sequence: [q | k | v] of its last token
+    last = np.cumsum(lengths) - 1
+    qkv = np.concatenate([c.qkv, c.rows[last]], 1)            # [n, q_dim + 2 kv_dim]
+    stride = q_dim + 2 * kv_dim
+    # device cache WITHOUT the step's tokens: append all other rows, poison stays in the step's slots
+    keep = np.ones(len(c.req), bool)
+    keep[last] = False
+    cache8 = torch.full(c.cache8.shape, 0x7F, dtype=torch.uint8, device=DEV)
+    scales = torch.full(c.scales.shape, float("nan"), dtype=torch.float32, device=DEV)
+    if keep.any():
+        fq.kv_append_fp8(cache8, scales, c.num_blocks, n_kv, dv(c.rows[keep]), 2 * kv_dim, 0, kv_dim, dv(c.bt), c.max_blocks,
+                         dv(c.req[keep]), dv(c.row_pos[keep]), int(keep.sum()))
+    out = torch.full((n, q_dim), 0x7FC0, dtype=torch.int16, device=DEV)
+    s = Scratch(n, n_kv * 4, c.max_blocks)
+    dq, meta = dv(qkv), (dv(c.pos), dv(c.qstart), dv(c.decode_rids), dv(c.bt))
+    for _ in range(3):
+        fq.append_attn_decode_fp8(cache8, scales, c.num_blocks, n_kv, dq, stride, 0, q_dim, q_dim + kv_dim, out, 128, meta[0],
+                                  meta[1], meta[2], None, n, meta[3], c.max_blocks, 16, c.scale, s.pm, s.pl, s.pa, s.slots,
+                                  flags=flags)
+    torch.cuda.synchronize()
+    fq.device_status()
+    got8, gots = host(cache8), host(scales)
+    written = ~np.isnan(c.scales)
+    assert np.array_equal(gots[written], c.scales[written]) and np.isnan(gots[~written]).all()
+    assert np.array_equal(got8, c.cache8), "cache bytes differ from fqb_kv_append_fp8's"
+    want = O.attn_decode_fp8(c.qkv, c.q_stride, c.cache8, c.scales, n_kv * 4, n_kv, c.pos, c.qstart, c.decode_rids, c.bt,
+                             c.scale, rows=n)
+    assert maxabs(host(out), want) <= TOL
