@@ -627,13 +627,23 @@ def run_fp8(a, dev, peak, peak_src):
     pm, pl, pa = torch.empty(slots, device=dev), torch.empty(slots, device=dev), torch.empty(slots * HD, device=dev)
     fq.device_status_reset()
 
-    fp8_flags = 0 if a.mode == "dependent" else INDEPENDENT   # --mode dependent: every launch waits for the one before it
+    # --mode dependent: every launch waits for the one before it; --mode fused: the engine-usable call (the
+    # step's token is quantised, stored and attended in the same kernel, FQB_DECODE_HISTORY_STABLE)
+    fp8_flags = {"dependent": 0, "fused": HISTORY_STABLE}.get(a.mode, INDEPENDENT)
+    qkv8 = None
+    if a.mode == "fused":
+        qkv8 = torch.randn((layers, a.batch, QKV_DIM), generator=g, device=dev).to(torch.bfloat16)
 
     def step():
         for layer in range(layers):
-            fq.attn_decode_fp8(q[layer], Q_DIM, pools[layer], scales[layer], num_blocks, out[layer], N_HEADS, N_KV, HD,
-                               pos_d, ar, ar, a.batch, bt_d, max_blocks, PAGE, HD ** -0.5, pm, pl, pa, slots, None,
-                               fp8_flags)
+            if qkv8 is not None:
+                fq.append_attn_decode_fp8(pools[layer], scales[layer], num_blocks, N_KV, qkv8[layer], QKV_DIM, 0, Q_DIM,
+                                          Q_DIM + KV_DIM, out[layer], HD, pos_d, ar, ar, None, a.batch, bt_d, max_blocks,
+                                          PAGE, HD ** -0.5, pm, pl, pa, slots, flags=fp8_flags)
+            else:
+                fq.attn_decode_fp8(q[layer], Q_DIM, pools[layer], scales[layer], num_blocks, out[layer], N_HEADS, N_KV, HD,
+                                   pos_d, ar, ar, a.batch, bt_d, max_blocks, PAGE, HD ** -0.5, pm, pl, pa, slots, None,
+                                   fp8_flags)
 
     ms, clocks = event_ms_with_clocks(dev.index or 0, step, max(a.steps, 10), a.warmup)
     fq.device_status()
@@ -659,7 +669,9 @@ def run_fp8(a, dev, peak, peak_src):
     return {"metric": "paged_decode_attn_kv_bytes_per_s", "value": round(gbs, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
             "dtype": "e4m3 KV (f16 MMA, fp32 accumulate)", "tokens_per_s_per_layer": round(a.batch / layer_s, 1),
             "config": {"workload": f"cfg2 over an fp8 cache: decode batch {a.batch}, ctx U[1,{a.max_ctx}], {layers} layers",
-                       "launches": "every launch waits for the one before it" if fp8_flags == 0 else "launches wait for nothing",
+                       "launches": {0: "every launch waits for the one before it",
+                                    HISTORY_STABLE: "fused append + attention, every launch waits for the one before it "
+                                                    "after it has requested its first pages"}.get(fp8_flags, "launches wait for nothing"),
                        "bytes_per_layer": nbytes, "sum_ctx": sum_ctx,
                        "l2": f"{layers} pools of 0.54 GB walked per step, larger than L2"},
             "clocks": clocks,
