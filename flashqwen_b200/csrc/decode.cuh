@@ -356,7 +356,7 @@ gather_publish_all_kernel(const PublishAllParams P) {
 // 128 dims and the order of the output dims are permuted so that every lane fetches 16 contiguous
 // bytes: lane (g, t) reads dims [32t, 32t+32) of its two key tokens for Q K^T, and dims [16g, 16g+16) of
 // its four value tokens for P V, whose accumulator columns then hold dims 32t+j and 32t+16+j.
-template <int NW, int NS, int HEADS, int MINB, int MAXD, bool FP8 = false, bool FP8_APPEND = false>
+template <int NW, int NS, int HEADS, int MINB, int MAXD, bool FP8 = false, bool APPEND = true>
 __global__ void __launch_bounds__(NW * 32, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
   using L = DecodeSmem<NW, NS, MAXD, FP8>;
@@ -654,8 +654,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
 #pragma unroll 1
     for (int page = cc.pb; page < cc.pe; ++page) {
       // fused append: this warp is the only one that streams the sequence's last page for this head
-      // (the fp8 kernel comes in two builds: the fused append costs the attention-only one registers it does not have)
-      const bool appends = (!FP8 || FP8_APPEND) && P.cache_w != nullptr && page == cc.np - 1;
+      // (every shape comes in two builds: where registers are short -- 168 per thread with three or six CTAs
+      // per SM -- the fused append's code costs the attention-only kernel a few per cent)
+      const bool appends = APPEND && P.cache_w != nullptr && page == cc.np - 1;
       uint4 new_row = make_uint4(0, 0, 0, 0);
       int a_blk = 0;
       if (appends) {  // lane -> plane = lane / 16 (K, V), 16-byte chunk lane % 16 of the head's 256-byte row
@@ -734,7 +735,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams P) {
           mma_bf16(o[2 * jj + 1], pa0, 0u, pa2, 0u, b2, b3);
         }
       } else {
-        if (FP8_APPEND && appends) {
+        if (appends) {
           // The step's token in the fp8 format: lanes 0..15 hold the K row of this head, lanes 16..31 the V
           // row, 8 values each; one scale per row (amax / 448), bytes e4m3(x * (448 / amax)) -- the
           // operations of kv_append_fp8_kernel, so the cache gets the same bytes. The row goes to the

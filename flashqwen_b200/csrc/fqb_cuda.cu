@@ -310,13 +310,17 @@ int launch_prefill(int max_qlen, int n_kv, int R, const CUtensorMap& map, const 
   return FQB_OK;
 }
 
+// The build with or without the fused append's code, by whether the call appends.
+#define FQB_LAUNCH(Cfg, FP8, ...) \
+  (cache_w ? launch_decode<Cfg, FP8, true>(__VA_ARGS__) : launch_decode<Cfg, FP8, false>(__VA_ARGS__))
+
 // ctas_per_sm: how many CTAs of THIS launch go on each SM (the kernel may allow more to be resident,
 // so that the CTAs of the launch after it can move in beside them).
-template <class Cfg, bool FP8 = false, bool FP8_APPEND = false>
+template <class Cfg, bool FP8 = false, bool APPEND = true>
 int launch_decode(const CUtensorMap& map, DecodeParams P, const int* rids, int n_decode, int sm_count,
                   int ctas_per_sm, bool pdl, cudaStream_t st) {
   using L = DecodeSmem<Cfg::NW, Cfg::NS, Cfg::MAXD, FP8>;
-  auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD, FP8, FP8_APPEND>;
+  auto kern = decode_kernel<Cfg::NW, Cfg::NS, Cfg::HEADS, Cfg::MINB, Cfg::MAXD, FP8, APPEND>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   FQB_CUDA_TRY(cudaGetDevice(&dev));
@@ -621,9 +625,9 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
         const int left = n_kv - base;
         P.kvh_base = base;
         int rc, took;
-        if (left >= 4) { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg4I, true, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<Decode8Cfg4I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st)) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
-        else if (left >= 2) { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg2I, true, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<Decode8Cfg2I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st)) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
-        else { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg1I, true, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : launch_decode<Decode8Cfg1I, true>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st)) : launch_decode<DecodeCfg1I>(map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
+        if (left >= 4) { rc = fp8 ? FQB_LAUNCH(Decode8Cfg4I, true, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : FQB_LAUNCH(DecodeCfg4, false, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 4; }
+        else if (left >= 2) { rc = fp8 ? FQB_LAUNCH(Decode8Cfg2I, true, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : FQB_LAUNCH(DecodeCfg2, false, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 2; }
+        else { rc = fp8 ? FQB_LAUNCH(Decode8Cfg1I, true, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st) : FQB_LAUNCH(DecodeCfg1I, false, map, P, decode_rids, n_decode, di.sm_count, 1, pdl, st); took = 1; }
         if (rc != FQB_OK) return rc;
         base += took;
         P.sync_first = 0;  // later launches of the call serve other heads: disjoint partials and counters
@@ -649,14 +653,14 @@ static int decode_impl(const void* q, int q_stride, const void* cache, int num_b
       // fp8, 8 heads, the launch waits: two head groups of four heads in one launch, three 4-warp CTAs per
       // SM (12 warps where the 8-head shape has 8; the kernel is bound by its issue rate, see Decode8Cfg4I)
       P.groups = 2;
-      rc = (cache_w ? launch_decode<Decode8Cfg4I, true, true>(map, P, decode_rids, n_decode, di.sm_count, 3, true, st) : launch_decode<Decode8Cfg4I, true>(map, P, decode_rids, n_decode, di.sm_count, 3, true, st));
+      rc = FQB_LAUNCH(Decode8Cfg4I, true, map, P, decode_rids, n_decode, di.sm_count, 3, true, st);
       P.groups = 1;
       took = 8;
     }
-    else if (left >= 8) { rc = launch_decode<DecodeCfg8>(map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
-    else if (left >= 4) { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg4, true, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<Decode8Cfg4, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st)) : launch_decode<DecodeCfg4>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
-    else if (left >= 2) { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg2, true, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<Decode8Cfg2, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st)) : launch_decode<DecodeCfg2>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
-    else { rc = fp8 ? (cache_w ? launch_decode<Decode8Cfg1, true, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : launch_decode<Decode8Cfg1, true>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st)) : launch_decode<DecodeCfg1>(map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
+    else if (left >= 8) { rc = FQB_LAUNCH(DecodeCfg8, false, map, P, decode_rids, n_decode, di.sm_count, 1, true, st); took = 8; }
+    else if (left >= 4) { rc = fp8 ? FQB_LAUNCH(Decode8Cfg4, true, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : FQB_LAUNCH(DecodeCfg4, false, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 4; }
+    else if (left >= 2) { rc = fp8 ? FQB_LAUNCH(Decode8Cfg2, true, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : FQB_LAUNCH(DecodeCfg2, false, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 2; }
+    else { rc = fp8 ? FQB_LAUNCH(Decode8Cfg1, true, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st) : FQB_LAUNCH(DecodeCfg1, false, map, P, decode_rids, n_decode, di.sm_count, kDefaultCtas, true, st); took = 1; }
     if (rc != FQB_OK) return rc;
     base += took;
     P.mode = kDecodeWaitFirst;
